@@ -1,0 +1,183 @@
+/*
+ * q35b — B200 (sm_100a) NVFP4 projection engine: C ABI.
+ *
+ * Drop-in boundary for the NVFP4 linear projections of the qwen35x runtime
+ * (reference: Danmoreng/qwen35x; citations are paths inside that project).
+ * Every function returns a q35b_status; on a nonzero status
+ * q35b_last_error() holds a human-readable message for the calling thread,
+ * mirroring the reference's `bool f(..., std::string & error_message)`
+ * convention (include/qwen35x/runtime/cuda_bench.h:7-283).
+ *
+ * Conventions
+ *   - N = output rows ("rows"), K = input columns ("cols"), M = tokens.
+ *   - Checkpoint ("ModelOpt") layout of a weight, as validated by the
+ *     reference in src/weights/modelopt_nvfp4.cpp:105-136:
+ *       codes   uint8 [N, K/2]   E2M1, element 2j in the low nibble
+ *       scales  uint8 [N, K/16]  E4M3, one per 16 K-elements
+ *       weight_scale_2 fp32, input_scale fp32
+ *   - All device pointers belong to the caller except the repacked weight,
+ *     which the engine owns.  No call below allocates or synchronises unless
+ *     it says so; every launch goes to the given stream.
+ *   - There is no CPU fallback: without a CUDA device every compute entry
+ *     point fails with Q35B_ERR_CUDA.
+ */
+#ifndef Q35B_NVFP4_H
+#define Q35B_NVFP4_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define Q35B_API
+#else
+#define Q35B_API __attribute__((visibility("default")))
+#endif
+
+typedef enum q35b_status {
+  Q35B_OK = 0,
+  Q35B_ERR_ARGUMENT = 1,    /* null pointer, bad count */
+  Q35B_ERR_SHAPE = 2,       /* dimensions the kernels do not support */
+  Q35B_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed (message has the call) */
+  Q35B_ERR_DEVICE_WAIT = 4, /* a bounded device-side wait expired */
+  Q35B_ERR_FORMAT = 5       /* tensor bytes violate the NVFP4 contract */
+} q35b_status;
+
+/* A weight repacked for the device.  Replaces the reference's
+ * PackedNvfp4Weight (src/runtime/qwen35x_cuda_backend.cpp:194-210) and its
+ * device twin Nvfp4Weight (src/kernels/cuda/weights.cuh:6-22). */
+typedef struct q35b_weight q35b_weight;
+
+/* CUDA stream handle (cudaStream_t) passed as an opaque pointer. */
+typedef void * q35b_stream;
+
+/* Kernel selector for the W4A16 decode projection; the names the CLI flag
+ * --nvfp4-projection-kernel accepts map onto these (reference:
+ * src/runtime/runtime.cpp:378-390, values 0..3 are the reference's). */
+typedef enum q35b_gemv_kernel {
+  Q35B_GEMV_AUTO = -1,
+  Q35B_GEMV_SIMT = 10,  /* 128-bit loads, in-register dequant, fp32 FMA, warp-shuffle reduction */
+  Q35B_GEMV_STREAM = 11 /* persistent, bulk-copy fed shared-memory ring */
+} q35b_gemv_kernel;
+
+/* ---- library ---------------------------------------------------------- */
+
+Q35B_API const char * q35b_last_error(void);
+Q35B_API const char * q35b_version(void);
+/* Number of kernels this library has launched in the calling process. */
+Q35B_API unsigned long long q35b_launch_count(void);
+
+/* ---- weights ---------------------------------------------------------- */
+
+/* Repack one checkpoint tensor family from HOST memory onto the current
+ * device.  Replaces load_modelopt_nvfp4_state's per-module repack
+ * (src/runtime/qwen35x_cuda_backend.cpp:1582-1695: pad_nvfp4_weight_for_tensor_core :967,
+ * swizzle_nvfp4_block_scale_for_tensor_core :990, pack_nvfp4_weight_for_sm120_mma :1029).
+ * Keeps rows [shard_index * ceil128(N / shard_count) ...) of the tensor: the
+ * shard boundaries are multiples of 128 rows except for the last shard.
+ * Allocates device memory and synchronises the legacy default stream. */
+Q35B_API int q35b_weight_create(const uint8_t * codes_host, const uint8_t * scales_host, float weight_scale_2,
+                                float input_scale, int n, int k, int shard_index, int shard_count,
+                                q35b_weight ** out);
+
+/* Same, from DEVICE buffers in checkpoint layout (the shard's rows are
+ * copied; the source may be freed afterwards). */
+Q35B_API int q35b_weight_create_from_device(const uint8_t * codes_dev, const uint8_t * scales_dev,
+                                            float weight_scale_2, float input_scale, int n, int k, int shard_index,
+                                            int shard_count, q35b_stream stream, q35b_weight ** out);
+
+Q35B_API void q35b_weight_destroy(q35b_weight * w);
+
+/* Shard geometry: first global row and row count held by this weight. */
+Q35B_API int q35b_weight_row_begin(const q35b_weight * w);
+Q35B_API int q35b_weight_rows(const q35b_weight * w);
+Q35B_API int q35b_weight_cols(const q35b_weight * w);
+/* Bytes one projection call streams from this weight (codes + scales). */
+Q35B_API size_t q35b_weight_stream_bytes(const q35b_weight * w);
+/* Row range of shard `shard_index` of an n-row tensor. */
+Q35B_API int q35b_shard_range(int n, int shard_index, int shard_count, int * row_begin, int * row_count);
+
+/* ---- decode: W4A16 projection, M = 1..8 ------------------------------- */
+
+/* y[m, r] = bf16( sum_c e2m1(w[r,c]) * e4m3(s[r,c/16]) * s2 * x[m, c] ), fp32
+ * accumulation, BF16 activations and output, input_scale not applied
+ * (the live decode of the reference passes 1.0,
+ * src/runtime/qwen35x_cuda_backend.cpp:2320).  Replaces matvec_nvfp4_bf16 /
+ * nvfp4_row_dot (src/kernels/cuda/decode_layers.cuh:200-284) and the scalar
+ * projection kernels (src/runtime/cuda_bench.cu:283-429).
+ * x: [m, K] bf16 device, y: [m, rows] bf16 device (rows = this shard's). */
+Q35B_API int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void * y_bf16, int kernel,
+                                  q35b_stream stream);
+
+/* The reference benchmark's contract (src/runtime/cuda_bench.cu:2042-2188):
+ * fp32 input of one token, activations multiplied by input_scale, fp32 output. */
+Q35B_API int q35b_gemv_w4a16_f32(const q35b_weight * w, const float * x_f32, float input_scale, float * y_f32,
+                                 int kernel, q35b_stream stream);
+
+/* ---- prefill: activation quantisation + W4A4 GEMM --------------------- */
+
+/* Scratch sizes for an [m, k] activation: packed codes m*k/2 bytes; tiled
+ * scales roundup(m,128) * roundup(k/16,4) bytes (the reference's rule,
+ * src/runtime/cuda_bench.cu:2616-2619). */
+Q35B_API size_t q35b_act_codes_bytes(int m, int k);
+Q35B_API size_t q35b_act_scales_bytes(int m, int k);
+/* Bytes of the quantiser's workspace; must be zero before its first use and
+ * is left zero by every call. */
+Q35B_API size_t q35b_quant_workspace_bytes(void);
+
+/* BF16 [m, k] -> NVFP4: E2M1 codes [m, k/2] (element 2j in the low nibble),
+ * E4M3 block scales in the 128x4 tiled layout, and the fp32 per-tensor scale
+ * g written to *input_scale_dev.  g = amax/(6*448) when global_scale <= 0,
+ * else global_scale.  Replaces nvfp4_quantize_bf16_matrix_for_cublaslt_kernel
+ * (src/runtime/cuda_bench.cu:178-213) and the two cudaMemset calls before it
+ * (:2621-2624). */
+Q35B_API int q35b_quantize_nvfp4_bf16(const void * x_bf16, int m, int k, float global_scale, uint8_t * codes,
+                                      uint8_t * scales_tiled, float * input_scale_dev, void * workspace,
+                                      q35b_stream stream);
+
+/* The reference's own activation recipe (no per-tensor scale, divisor =
+ * unrounded block scale, src/runtime/cuda_bench.cu:178-213), kept so the
+ * quantiser can be checked byte-for-byte against the reference's kernel.
+ * swap_nibbles != 0 writes element 2j in the HIGH nibble as that kernel does. */
+Q35B_API int q35b_quantize_nvfp4_bf16_reference_recipe(const void * x_bf16, int m, int k, int swap_nibbles,
+                                                       uint8_t * codes, uint8_t * scales_tiled,
+                                                       q35b_stream stream);
+
+/* c[m, rows] (bf16, row stride ldc elements) = (Aq . Wq^T) * g * s2 with
+ * tcgen05 block-scaled FP4 MMA.  Replaces
+ * run_nvfp4_cublaslt_prefill_projection_device (src/runtime/cuda_bench.cu:1056-1167)
+ * and the fp32->bf16 pass after it (src/kernels/cuda/prefill.cu:639).
+ * Requires k % 64 == 0.  status_dev: 4 bytes of device memory, zero on entry,
+ * nonzero afterwards if a bounded device-side wait expired (may be NULL). */
+Q35B_API int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
+                                 const float * input_scale_dev, int m, void * c_bf16, int ldc,
+                                 unsigned int * status_dev, q35b_stream stream);
+
+/* ---- synthetic checkpoints ---------------------------------------------- */
+
+/* fp32 [n, k] -> NVFP4 in checkpoint layout (codes [n, k/2], row-major scales
+ * [n, k/16]) with weight_scale_2 = amax/(6*448) written to *s2_dev, the
+ * recipe of q35b_quantize_nvfp4_bf16.  The reference has no weight quantiser
+ * (it consumes pre-quantised ModelOpt checkpoints, docs/development_plan.md:389);
+ * this exists to build synthetic tensors for benchmarks and tests. */
+Q35B_API int q35b_quantize_weight_f32(const float * w_f32, int n, int k, uint8_t * codes, uint8_t * scales,
+                                      float * s2_dev, void * workspace, q35b_stream stream);
+
+/* ---- host twins of the device codecs (no GPU needed) ------------------- */
+
+/* The encoders/decoders the kernels use, compiled for the host, so their
+ * equivalence with the reference's scan encoders
+ * (src/runtime/cuda_bench.cu:902-940) can be checked on any machine. */
+Q35B_API uint8_t q35b_debug_encode_ue4m3(float v);
+Q35B_API uint8_t q35b_debug_encode_e2m1(float v);
+Q35B_API float q35b_debug_decode_e4m3(uint8_t b);
+Q35B_API float q35b_debug_decode_e2m1(uint8_t c);
+Q35B_API long long q35b_debug_tiled_scale_offset(int row, int col, int padded_cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q35B_NVFP4_H */

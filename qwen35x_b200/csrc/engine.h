@@ -1,0 +1,72 @@
+// Internal declarations shared by the translation units of libq35b.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <string>
+
+#include "../../include/q35b_nvfp4.h"
+
+namespace q35b {
+
+// Thread-local message behind q35b_last_error().
+void set_error(const std::string & message);
+int fail(int status, const std::string & message);
+int fail_cuda(cudaError_t e, const char * what);
+
+#define Q35B_CUDA_TRY(call, what)                                 \
+  do {                                                            \
+    const cudaError_t q35b_e_ = (call);                           \
+    if (q35b_e_ != cudaSuccess) return ::q35b::fail_cuda(q35b_e_, what); \
+  } while (0)
+
+extern std::atomic<unsigned long long> g_launches;
+inline void count_launch(unsigned n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int sm_count();
+
+}  // namespace q35b
+
+// One projection weight on the device.  All three arrays live in a single
+// allocation; codes and both scale layouts are 256-byte aligned.
+struct q35b_weight {
+  int n_total = 0;    // rows of the whole tensor
+  int k = 0;          // columns
+  int row_begin = 0;  // first global row of this shard
+  int rows = 0;       // rows held
+  float s2 = 1.0f;    // weight_scale_2
+  float input_scale = 1.0f;
+  int device = 0;
+  void * base = nullptr;            // the allocation
+  uint8_t * codes = nullptr;        // [rows, k/2], checkpoint order (K-major: also the UMMA B operand)
+  uint8_t * scales = nullptr;       // [rows, k/16] row-major (decode kernels)
+  uint8_t * scales_tiled = nullptr; // [ceil128(rows), ceil4(k/16)] 128x4 tiles (UMMA scale factors)
+  size_t codes_bytes = 0, scales_bytes = 0, scales_tiled_bytes = 0;
+  bool has_tmap = false;
+  alignas(64) CUtensorMap tmap_codes;  // 2-D map over codes for the GEMM's B tiles
+  int tmap_block_n = 0;
+};
+
+namespace q35b {
+
+// gemv_w4a16.cu
+int launch_gemv_bf16(const q35b_weight * w, const void * x_bf16, int m, void * y_bf16, int kernel, cudaStream_t s);
+int launch_gemv_f32(const q35b_weight * w, const float * x, float input_scale, float * y, int kernel, cudaStream_t s);
+
+// act_quant.cu
+int launch_quantize_bf16(const void * x, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
+                         float * g_dev, void * workspace, cudaStream_t s);
+int launch_quantize_reference_recipe(const void * x, int m, int k, int swap, uint8_t * codes, uint8_t * scales_tiled,
+                                     cudaStream_t s);
+int launch_quantize_weight_f32(const float * w, int n, int k, uint8_t * codes, uint8_t * scales_rowmajor,
+                               float * s2_dev, void * workspace, cudaStream_t s);
+int launch_tile_scales(const uint8_t * scales_rowmajor, int rows, int scale_cols, uint8_t * tiled, cudaStream_t s);
+
+// gemm_w4a4_tcgen05.cu
+int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+                     int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s);
+
+}  // namespace q35b

@@ -1,0 +1,264 @@
+"""ctypes binding of libq35b.so plus thin torch helpers.
+
+torch is used for device memory and streams only; every computation goes
+through the C ABI.  There is no CPU fallback: if the library is missing or no
+CUDA device is present, calls raise."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+_PKG = Path(__file__).resolve().parent
+_LIB_PATH = _PKG / "_lib" / "libq35b.so"
+_lib = None
+
+GEMV_AUTO, GEMV_SIMT, GEMV_STREAM = -1, 10, 11
+
+
+class Q35bError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"q35b status {status}: {message}")
+        self.status = status
+
+
+def lib() -> C.CDLL:
+    """Load libq35b.so (built by `python -m qwen35x_b200.build`); raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.is_file():
+        raise FileNotFoundError(f"{_LIB_PATH} is missing: run `python -m qwen35x_b200.build` (needs nvcc)")
+    L = C.CDLL(str(_LIB_PATH))
+    vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+    L.q35b_last_error.restype = C.c_char_p
+    L.q35b_version.restype = C.c_char_p
+    L.q35b_launch_count.restype = C.c_ulonglong
+    L.q35b_weight_create.restype = i
+    L.q35b_weight_create.argtypes = [vp, vp, f, f, i, i, i, i, C.POINTER(vp)]
+    L.q35b_weight_create_from_device.restype = i
+    L.q35b_weight_create_from_device.argtypes = [vp, vp, f, f, i, i, i, i, vp, C.POINTER(vp)]
+    L.q35b_weight_destroy.restype = None
+    L.q35b_weight_destroy.argtypes = [vp]
+    for name in ("q35b_weight_row_begin", "q35b_weight_rows", "q35b_weight_cols"):
+        getattr(L, name).restype = i
+        getattr(L, name).argtypes = [vp]
+    L.q35b_weight_stream_bytes.restype = sz
+    L.q35b_weight_stream_bytes.argtypes = [vp]
+    L.q35b_shard_range.restype = i
+    L.q35b_shard_range.argtypes = [i, i, i, C.POINTER(i), C.POINTER(i)]
+    L.q35b_gemv_w4a16_bf16.restype = i
+    L.q35b_gemv_w4a16_bf16.argtypes = [vp, vp, i, vp, i, vp]
+    L.q35b_gemv_w4a16_f32.restype = i
+    L.q35b_gemv_w4a16_f32.argtypes = [vp, vp, f, vp, i, vp]
+    L.q35b_act_codes_bytes.restype = sz
+    L.q35b_act_codes_bytes.argtypes = [i, i]
+    L.q35b_act_scales_bytes.restype = sz
+    L.q35b_act_scales_bytes.argtypes = [i, i]
+    L.q35b_quant_workspace_bytes.restype = sz
+    L.q35b_quantize_nvfp4_bf16.restype = i
+    L.q35b_quantize_nvfp4_bf16.argtypes = [vp, i, i, f, vp, vp, vp, vp, vp]
+    L.q35b_quantize_nvfp4_bf16_reference_recipe.restype = i
+    L.q35b_quantize_nvfp4_bf16_reference_recipe.argtypes = [vp, i, i, i, vp, vp, vp]
+    L.q35b_quantize_weight_f32.restype = i
+    L.q35b_quantize_weight_f32.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
+    L.q35b_gemm_w4a4_bf16.restype = i
+    L.q35b_gemm_w4a4_bf16.argtypes = [vp, vp, vp, vp, i, vp, i, vp, vp]
+    L.q35b_debug_encode_ue4m3.restype = C.c_uint8
+    L.q35b_debug_encode_ue4m3.argtypes = [f]
+    L.q35b_debug_encode_e2m1.restype = C.c_uint8
+    L.q35b_debug_encode_e2m1.argtypes = [f]
+    L.q35b_debug_decode_e4m3.restype = f
+    L.q35b_debug_decode_e4m3.argtypes = [C.c_uint8]
+    L.q35b_debug_decode_e2m1.restype = f
+    L.q35b_debug_decode_e2m1.argtypes = [C.c_uint8]
+    L.q35b_debug_tiled_scale_offset.restype = C.c_longlong
+    L.q35b_debug_tiled_scale_offset.argtypes = [i, i, i]
+    _lib = L
+    return L
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise Q35bError(status, lib().q35b_last_error().decode("utf-8", "replace"))
+
+
+def launch_count() -> int:
+    return int(lib().q35b_launch_count())
+
+
+def shard_range(n: int, shard_index: int, shard_count: int) -> tuple[int, int]:
+    b, c = C.c_int(0), C.c_int(0)
+    _check(lib().q35b_shard_range(n, shard_index, shard_count, C.byref(b), C.byref(c)))
+    return b.value, c.value
+
+
+def _torch():
+    import torch
+
+    if not torch.cuda.is_available():
+        raise Q35bError(3, "no CUDA device: the NVFP4 projection engine has no CPU fallback")
+    return torch
+
+
+def _stream_ptr(torch) -> int:
+    return int(torch.cuda.current_stream().cuda_stream)
+
+
+class Nvfp4Weight:
+    """One projection weight (or one row shard of it) repacked on the current CUDA device.
+
+    Mirrors the role of the reference's PackedNvfp4Weight
+    (src/runtime/qwen35x_cuda_backend.cpp:194-210)."""
+
+    def __init__(self, handle: int, n: int, k: int, s2: float, input_scale: float):
+        self._h = C.c_void_p(handle)
+        self.n_total, self.k, self.s2, self.input_scale = n, k, s2, input_scale
+        L = lib()
+        self.row_begin = L.q35b_weight_row_begin(self._h)
+        self.rows = L.q35b_weight_rows(self._h)
+        self.stream_bytes = int(L.q35b_weight_stream_bytes(self._h))
+
+    @classmethod
+    def from_host(cls, codes: np.ndarray, scales: np.ndarray, weight_scale_2: float, input_scale: float = 1.0,
+                  shard_index: int = 0, shard_count: int = 1) -> "Nvfp4Weight":
+        _torch()
+        codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        scales = np.ascontiguousarray(scales, dtype=np.uint8)
+        n, k = codes.shape[0], codes.shape[1] * 2
+        if scales.shape != (n, k // 16):
+            raise Q35bError(2, "NVFP4 packed weight or scale size does not match matrix dimensions.")
+        h = C.c_void_p()
+        _check(lib().q35b_weight_create(codes.ctypes.data, scales.ctypes.data, weight_scale_2, input_scale, n, k,
+                                        shard_index, shard_count, C.byref(h)))
+        return cls(h.value, n, k, weight_scale_2, input_scale)
+
+    @classmethod
+    def from_device(cls, codes, scales, weight_scale_2: float, input_scale: float = 1.0, shard_index: int = 0,
+                    shard_count: int = 1) -> "Nvfp4Weight":
+        torch = _torch()
+        assert codes.is_cuda and scales.is_cuda and codes.dtype == torch.uint8 and scales.dtype == torch.uint8
+        codes, scales = codes.contiguous(), scales.contiguous()
+        n, k = codes.shape[0], codes.shape[1] * 2
+        if tuple(scales.shape) != (n, k // 16):
+            raise Q35bError(2, "NVFP4 packed weight or scale size does not match matrix dimensions.")
+        h = C.c_void_p()
+        _check(lib().q35b_weight_create_from_device(codes.data_ptr(), scales.data_ptr(), weight_scale_2, input_scale,
+                                                    n, k, shard_index, shard_count, _stream_ptr(torch), C.byref(h)))
+        return cls(h.value, n, k, weight_scale_2, input_scale)
+
+    @property
+    def handle(self) -> C.c_void_p:
+        return self._h
+
+    def close(self) -> None:
+        if self._h is not None and self._h.value:
+            lib().q35b_weight_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def gemv_w4a16(weight: Nvfp4Weight, x, out=None, kernel: int = GEMV_AUTO):
+    """Decode projection: x [m, K] bf16 (m = 1..8) -> y [m, rows] bf16."""
+    torch = _torch()
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == weight.k
+    m = x.shape[0]
+    if out is None:
+        out = torch.empty((m, weight.rows), dtype=torch.bfloat16, device=x.device)
+    _check(lib().q35b_gemv_w4a16_bf16(weight.handle, x.data_ptr(), m, out.data_ptr(), kernel, _stream_ptr(torch)))
+    return out
+
+
+def gemv_w4a16_f32(weight: Nvfp4Weight, x, input_scale: float = 1.0, out=None, kernel: int = GEMV_AUTO):
+    """The reference benchmark's contract: fp32 x [K], fp32 y [rows], x scaled by input_scale."""
+    torch = _torch()
+    assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.numel() == weight.k
+    if out is None:
+        out = torch.empty((weight.rows,), dtype=torch.float32, device=x.device)
+    _check(lib().q35b_gemv_w4a16_f32(weight.handle, x.data_ptr(), input_scale, out.data_ptr(), kernel,
+                                     _stream_ptr(torch)))
+    return out
+
+
+_workspaces: dict = {}
+
+
+def _workspace(torch, device):
+    key = (device.index, int(torch.cuda.current_stream().cuda_stream))
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(int(lib().q35b_quant_workspace_bytes()), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def act_scratch(m: int, k: int, device):
+    """Caller-owned scratch for an [m, k] activation: (codes, tiled scales, input-scale word)."""
+    torch = _torch()
+    L = lib()
+    codes = torch.empty(int(L.q35b_act_codes_bytes(m, k)), dtype=torch.uint8, device=device)
+    scales = torch.empty(int(L.q35b_act_scales_bytes(m, k)), dtype=torch.uint8, device=device)
+    g = torch.empty(1, dtype=torch.float32, device=device)
+    return codes, scales, g
+
+
+def quantize_activations(x, global_scale: float = 0.0, scratch=None):
+    """BF16 [m, k] -> (codes [m, k/2] u8, tiled scales u8, g fp32[1]) on the device."""
+    torch = _torch()
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 2
+    m, k = x.shape
+    codes, scales, g = scratch if scratch is not None else act_scratch(m, k, x.device)
+    ws = _workspace(torch, x.device)
+    _check(lib().q35b_quantize_nvfp4_bf16(x.data_ptr(), m, k, global_scale, codes.data_ptr(), scales.data_ptr(),
+                                          g.data_ptr(), ws.data_ptr(), _stream_ptr(torch)))
+    return codes.view(m, k // 2), scales, g
+
+
+def quantize_activations_reference_recipe(x, swap_nibbles: bool = True):
+    torch = _torch()
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 2
+    m, k = x.shape
+    codes, scales, _ = act_scratch(m, k, x.device)
+    _check(lib().q35b_quantize_nvfp4_bf16_reference_recipe(x.data_ptr(), m, k, int(swap_nibbles), codes.data_ptr(),
+                                                           scales.data_ptr(), _stream_ptr(torch)))
+    return codes.view(m, k // 2), scales
+
+
+def quantize_weight(w_f32):
+    """fp32 [n, k] on the device -> (codes [n, k/2], scales [n, k/16] row-major, s2 float)."""
+    torch = _torch()
+    assert w_f32.is_cuda and w_f32.dtype == torch.float32 and w_f32.is_contiguous() and w_f32.dim() == 2
+    n, k = w_f32.shape
+    codes = torch.empty((n, k // 2), dtype=torch.uint8, device=w_f32.device)
+    scales = torch.empty((n, k // 16), dtype=torch.uint8, device=w_f32.device)
+    s2 = torch.empty(1, dtype=torch.float32, device=w_f32.device)
+    ws = _workspace(torch, w_f32.device)
+    _check(lib().q35b_quantize_weight_f32(w_f32.data_ptr(), n, k, codes.data_ptr(), scales.data_ptr(), s2.data_ptr(),
+                                          ws.data_ptr(), _stream_ptr(torch)))
+    return codes, scales, float(s2.item())
+
+
+def gemm_w4a4(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, out=None, status=None):
+    """Prefill projection on quantised activations: -> c [m, rows] bf16."""
+    torch = _torch()
+    if out is None:
+        out = torch.empty((m, weight.rows), dtype=torch.bfloat16, device=a_codes.device)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+    _check(lib().q35b_gemm_w4a4_bf16(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(), g.data_ptr(), m,
+                                     out.data_ptr(), out.stride(0), status.data_ptr() if status is not None else None,
+                                     _stream_ptr(torch)))
+    return out
+
+
+def project_prefill(weight: Nvfp4Weight, x, out=None, scratch=None, global_scale: float = 0.0):
+    """BF16 [m, K] -> BF16 [m, rows]: activation quantisation followed by the W4A4 GEMM."""
+    codes, scales, g = quantize_activations(x, global_scale, scratch)
+    return gemm_w4a4(weight, codes, scales, g, x.shape[0], out)
