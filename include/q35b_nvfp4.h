@@ -156,6 +156,28 @@ Q35B_API int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes,
                                  const float * input_scale_dev, int m, void * c_bf16, int ldc,
                                  unsigned int * status_dev, q35b_stream stream);
 
+/* Prefill projection for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * bridges all take caller-allocated scratch, include/qwen35x/runtime/cuda_bench.h:70-83).
+ *
+ * c[m, rows] (bf16, row stride ldc) = NVFP4-quantise(x[m, K]) projected through w: the same two kernels as
+ * q35b_quantize_nvfp4_bf16 followed by q35b_gemm_w4a4_bf16, but the quantised activation, its scales, the
+ * per-tensor scale word, the quantiser workspace and the status word live in a scratch area built into the
+ * library (a file-scope device array, 24 MiB, held by every GPU that loads the library until the process exits).
+ * It is meant for hosts that own all device memory themselves (a pre-sized arena, a fixed memory budget) or that
+ * must not hit the device-wide synchronisation an allocation implies.  The call itself makes no cudaMalloc,
+ * cudaFree or other allocating call.
+ *
+ *  - m * K / 2 (rounded up to 256) + roundup(m,128) * roundup(K/16,4) must fit in
+ *    q35b_static_prefill_capacity_bytes(); larger activations are rejected with Q35B_ERR_SHAPE.
+ *  - The first call on each device resolves the scratch's device address (and sets kernel attributes): make that
+ *    first call outside any stream capture.
+ *  - All calls on a device share the one scratch area: two calls that may overlap on the GPU (different streams
+ *    without an ordering between them, or different threads) race on it.  Serialise them.
+ *  - The area keeps the previous call's bytes; the words that must start at zero are cleared by every call. */
+Q35B_API size_t q35b_static_prefill_capacity_bytes(void);
+Q35B_API int q35b_project_prefill_bf16_static(const q35b_weight * w, const void * x_bf16, int m, float global_scale,
+                                              void * c_bf16, int ldc, q35b_stream stream);
+
 /* ---- synthetic checkpoints ---------------------------------------------- */
 
 /* fp32 [n, k] -> NVFP4 in checkpoint layout (codes [n, k/2], row-major scales

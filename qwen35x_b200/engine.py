@@ -65,6 +65,9 @@ def lib() -> C.CDLL:
     L.q35b_quantize_weight_f32.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
     L.q35b_gemm_w4a4_bf16.restype = i
     L.q35b_gemm_w4a4_bf16.argtypes = [vp, vp, vp, vp, i, vp, i, vp, vp]
+    L.q35b_static_prefill_capacity_bytes.restype = sz
+    L.q35b_project_prefill_bf16_static.restype = i
+    L.q35b_project_prefill_bf16_static.argtypes = [vp, vp, i, f, vp, i, vp]
     L.q35b_debug_encode_ue4m3.restype = C.c_uint8
     L.q35b_debug_encode_ue4m3.argtypes = [f]
     L.q35b_debug_encode_e2m1.restype = C.c_uint8
@@ -262,3 +265,16 @@ def project_prefill(weight: Nvfp4Weight, x, out=None, scratch=None, global_scale
     """BF16 [m, K] -> BF16 [m, rows]: activation quantisation followed by the W4A4 GEMM."""
     codes, scales, g = quantize_activations(x, global_scale, scratch)
     return gemm_w4a4(weight, codes, scales, g, x.shape[0], out)
+
+
+def project_prefill_static(weight: Nvfp4Weight, x, out=None, global_scale: float = 0.0):
+    """project_prefill for hosts that cannot allocate: the activation scratch is the library's built-in device
+    array (see q35b_project_prefill_bf16_static in include/q35b_nvfp4.h).  Calls sharing a device must not overlap."""
+    torch = _torch()
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 2 and x.shape[1] == weight.k
+    m = x.shape[0]
+    if out is None:
+        out = torch.empty((m, weight.rows), dtype=torch.bfloat16, device=x.device)
+    _check(lib().q35b_project_prefill_bf16_static(weight.handle, x.data_ptr(), m, global_scale, out.data_ptr(),
+                                                  out.stride(0), _stream_ptr(torch)))
+    return out
