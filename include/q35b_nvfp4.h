@@ -60,7 +60,7 @@ typedef void * q35b_stream;
 typedef enum q35b_gemv_kernel {
   Q35B_GEMV_AUTO = -1,
   Q35B_GEMV_SIMT = 10,  /* 128-bit loads, in-register dequant, fp32 FMA, warp-shuffle reduction */
-  Q35B_GEMV_STREAM = 11 /* persistent, bulk-copy fed shared-memory ring */
+  Q35B_GEMV_STREAM = 11 /* persistent, TMA-fed shared-memory ring; first use per (weight, m) allocates its work list */
 } q35b_gemv_kernel;
 
 /* ---- library ---------------------------------------------------------- */
@@ -116,6 +116,28 @@ Q35B_API int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, in
  * fp32 input of one token, activations multiplied by input_scale, fp32 output. */
 Q35B_API int q35b_gemv_w4a16_f32(const q35b_weight * w, const float * x_f32, float input_scale, float * y_f32,
                                  int kernel, q35b_stream stream);
+
+/* One persistent launch over several independent projections (the work list of a decode step, or of one phase of
+ * it).  Replaces the per-phase matvec loops of the reference's persistent decode kernel
+ * (src/kernels/cuda/decode_kernel.cuh:58-84).  Every weight needs cols % 256 == 0 and unsigned block scales.
+ * The items are independent: no projection may read another one's output in the same run. */
+typedef struct q35b_gemv_item {
+  const q35b_weight * weight;
+  const void * x_bf16; /* [m, K] device */
+  void * y_bf16;       /* [m, rows] device */
+} q35b_gemv_item;
+
+typedef struct q35b_gemv_batch q35b_gemv_batch;
+/* Builds the tile schedule and uploads the descriptors (allocates, synchronises). */
+Q35B_API int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out);
+/* One kernel launch on `stream`; no allocation, no synchronisation. */
+Q35B_API int q35b_gemv_batch_run(const q35b_gemv_batch * batch, q35b_stream stream);
+Q35B_API void q35b_gemv_batch_destroy(q35b_gemv_batch * batch);
+/* Copies the batch's device status word to the host (synchronises): 0, or the code of a bounded device-side wait
+ * that expired during a run. */
+Q35B_API int q35b_gemv_batch_status(const q35b_gemv_batch * batch, unsigned int * status_out);
+/* Weight bytes (codes + scales) one run streams. */
+Q35B_API size_t q35b_gemv_batch_stream_bytes(const q35b_gemv_batch * batch);
 
 /* ---- prefill: activation quantisation + W4A4 GEMM --------------------- */
 

@@ -195,7 +195,7 @@ quantize_nvfp4_kernel(const T * __restrict__ x, int rows, int rows_padded, int k
 
 __global__ void __launch_bounds__(kThreads)
 tile_scales_kernel(const uint8_t * __restrict__ src, int rows, int rows_padded, int scale_cols,
-                   uint8_t * __restrict__ tiled) {
+                   uint8_t * __restrict__ tiled, unsigned int * __restrict__ sign_flag) {
   const int groups = (scale_cols + 3) >> 2;
   const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<size_t>(rows_padded) * groups) return;
@@ -210,6 +210,7 @@ tile_scales_kernel(const uint8_t * __restrict__ src, int rows, int rows_padded, 
     }
   }
   *reinterpret_cast<uint32_t *>(tiled + tiled_scale_offset(row, grp * 4, groups * 4)) = sbytes;
+  if (sign_flag != nullptr && (sbytes & 0x80808080u) != 0u) atomicOr(sign_flag, 1u);
 }
 
 int check_quant_args(const void * x, int m, int k, const void * codes, const void * scales) {
@@ -286,11 +287,12 @@ int launch_quantize_weight_f32(const float * w, int n, int k, uint8_t * codes, u
   return Q35B_OK;
 }
 
-int launch_tile_scales(const uint8_t * scales_rowmajor, int rows, int scale_cols, uint8_t * tiled, cudaStream_t s) {
+int launch_tile_scales(const uint8_t * scales_rowmajor, int rows, int scale_cols, uint8_t * tiled,
+                       unsigned int * sign_flag, cudaStream_t s) {
   const int rows_padded = round_up_int(rows, 128);
   const size_t threads = static_cast<size_t>(rows_padded) * ((scale_cols + 3) >> 2);
   const unsigned blocks = static_cast<unsigned>((threads + kThreads - 1) / kThreads);
-  tile_scales_kernel<<<blocks, kThreads, 0, s>>>(scales_rowmajor, rows, rows_padded, scale_cols, tiled);
+  tile_scales_kernel<<<blocks, kThreads, 0, s>>>(scales_rowmajor, rows, rows_padded, scale_cols, tiled, sign_flag);
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "tile_scales_kernel launch");
   return Q35B_OK;

@@ -69,7 +69,7 @@ int alloc_weight(int n, int k, int shard_index, int shard_count, float s2, float
   w->scales_tiled_bytes = static_cast<size_t>(round_up_int(std::max(count, 1), 128)) * round_up_int(k / 16, 4);
   const size_t o_scales = align_up(w->codes_bytes, 256);
   const size_t o_tiled = o_scales + align_up(w->scales_bytes, 256);
-  const size_t total = o_tiled + align_up(w->scales_tiled_bytes, 256);
+  const size_t total = o_tiled + align_up(w->scales_tiled_bytes, 256) + 256;  // + one control block
   const cudaError_t e = cudaMalloc(&w->base, total);
   if (e != cudaSuccess) {
     delete w;
@@ -132,6 +132,12 @@ int q35b_weight_create(const uint8_t * codes_host, const uint8_t * scales_host, 
       tiled[static_cast<size_t>(tiled_scale_offset(r, c, padded_cols))] = src_scales[static_cast<size_t>(r) * scale_cols + c];
     }
   }
+  for (size_t i = 0; i < w->scales_bytes; ++i) {
+    if (src_scales[i] & 0x80u) {
+      w->negative_scales = true;
+      break;
+    }
+  }
   cudaError_t e = cudaSuccess;
   if (w->rows > 0) {
     e = cudaMemcpy(w->codes, src_codes, w->codes_bytes, cudaMemcpyHostToDevice);
@@ -171,21 +177,34 @@ int q35b_weight_create_from_device(const uint8_t * codes_dev, const uint8_t * sc
     q35b_weight_destroy(w);
     return fail_cuda(e, "cudaMemcpyAsync(nvfp4 weight)");
   }
-  if (const int st = launch_tile_scales(w->scales, w->rows, scale_cols, w->scales_tiled, s)) {
+  auto * sign_flag = reinterpret_cast<unsigned int *>(w->scales_tiled + align_up(w->scales_tiled_bytes, 256));
+  e = cudaMemsetAsync(sign_flag, 0, sizeof(unsigned int), s);
+  if (e != cudaSuccess) {
+    q35b_weight_destroy(w);
+    return fail_cuda(e, "cudaMemsetAsync(nvfp4 weight)");
+  }
+  if (const int st = launch_tile_scales(w->scales, w->rows, scale_cols, w->scales_tiled, sign_flag, s)) {
     q35b_weight_destroy(w);
     return st;
   }
-  e = cudaStreamSynchronize(s);
+  unsigned int flag = 0;
+  e = cudaMemcpyAsync(&flag, sign_flag, sizeof(flag), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) {
     q35b_weight_destroy(w);
     return fail_cuda(e, "cudaStreamSynchronize(nvfp4 weight)");
   }
+  w->negative_scales = flag != 0;
   *out = w;
   return Q35B_OK;
 }
 
 void q35b_weight_destroy(q35b_weight * w) {
   if (w == nullptr) return;
+  for (auto *& b : w->stream_batch) {
+    gemv_batch_free(b);
+    b = nullptr;
+  }
   if (w->base != nullptr) cudaFree(w->base);
   delete w;
 }
@@ -197,8 +216,38 @@ size_t q35b_weight_stream_bytes(const q35b_weight * w) { return w ? w->codes_byt
 
 int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void * y_bf16, int kernel,
                          q35b_stream stream) {
+  if (kernel == Q35B_GEMV_STREAM) {
+    if (w == nullptr || x_bf16 == nullptr || y_bf16 == nullptr) {
+      return fail(Q35B_ERR_ARGUMENT, "NVFP4 projection received a null buffer.");
+    }
+    if (m < 1 || m > 8) return fail(Q35B_ERR_SHAPE, "NVFP4 decode projection supports 1..8 tokens.");
+    if (w->rows == 0) return Q35B_OK;
+    auto * wm = const_cast<q35b_weight *>(w);
+    if (wm->stream_batch[m] == nullptr) {
+      // first use with this token count: build (and upload) the single-projection work list
+      q35b_gemv_item item{w, nullptr, nullptr};
+      if (const int st = gemv_batch_build(&item, 1, m, &wm->stream_batch[m])) return st;
+    }
+    return gemv_batch_launch(wm->stream_batch[m], x_bf16, y_bf16, static_cast<cudaStream_t>(stream));
+  }
   return launch_gemv_bf16(w, x_bf16, m, y_bf16, kernel, static_cast<cudaStream_t>(stream));
 }
+
+int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out) {
+  return gemv_batch_build(items, count, m, out);
+}
+
+int q35b_gemv_batch_run(const q35b_gemv_batch * batch, q35b_stream stream) {
+  return gemv_batch_launch(batch, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+void q35b_gemv_batch_destroy(q35b_gemv_batch * batch) { gemv_batch_free(batch); }
+
+int q35b_gemv_batch_status(const q35b_gemv_batch * batch, unsigned int * status_out) {
+  return gemv_batch_read_status(batch, status_out);
+}
+
+size_t q35b_gemv_batch_stream_bytes(const q35b_gemv_batch * batch) { return gemv_batch_bytes(batch); }
 
 int q35b_gemv_w4a16_f32(const q35b_weight * w, const float * x_f32, float input_scale, float * y_f32, int kernel,
                         q35b_stream stream) {

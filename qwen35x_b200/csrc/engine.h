@@ -45,6 +45,8 @@ struct q35b_weight {
   uint8_t * scales = nullptr;       // [rows, k/16] row-major (decode kernels)
   uint8_t * scales_tiled = nullptr; // [ceil128(rows), ceil4(k/16)] 128x4 tiles (UMMA scale factors)
   size_t codes_bytes = 0, scales_bytes = 0, scales_tiled_bytes = 0;
+  bool negative_scales = false;      // some block scale has its sign bit set (only the SIMT decode kernel takes those)
+  struct q35b_gemv_batch * stream_batch[9] = {nullptr};  // lazily built single-projection work lists, by token count
   bool has_tmap = false;
   alignas(64) CUtensorMap tmap_codes;  // 2-D map over codes for the GEMM's B tiles
   int tmap_block_n = 0;
@@ -63,9 +65,19 @@ int launch_quantize_reference_recipe(const void * x, int m, int k, int swap, uin
                                      cudaStream_t s);
 int launch_quantize_weight_f32(const float * w, int n, int k, uint8_t * codes, uint8_t * scales_rowmajor,
                                float * s2_dev, void * workspace, cudaStream_t s);
-int launch_tile_scales(const uint8_t * scales_rowmajor, int rows, int scale_cols, uint8_t * tiled, cudaStream_t s);
+int launch_tile_scales(const uint8_t * scales_rowmajor, int rows, int scale_cols, uint8_t * tiled,
+                       unsigned int * sign_flag, cudaStream_t s);
+
+// gemv_stream.cu
+bool gemv_stream_eligible(const q35b_weight * w, int m);
+int gemv_batch_build(const q35b_gemv_item * items, int count, int m, struct q35b_gemv_batch ** out);
+int gemv_batch_launch(const struct q35b_gemv_batch * b, const void * x_override, void * y_override, cudaStream_t s);
+void gemv_batch_free(struct q35b_gemv_batch * b);
+int gemv_batch_read_status(const struct q35b_gemv_batch * b, unsigned int * out);
+size_t gemv_batch_bytes(const struct q35b_gemv_batch * b);
 
 // gemm_w4a4_tcgen05.cu
+int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, int box_rows);
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s);
 

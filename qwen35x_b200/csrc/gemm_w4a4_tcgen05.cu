@@ -354,6 +354,8 @@ gemm_w4a4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
 // ---- host side ---------------------------------------------------------------
 
+}  // namespace
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -373,6 +375,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D map over a K-major code matrix [rows, k_bytes] of bytes; box = box_rows x 128 bytes, 128B swizzle.
+// Shared with the streaming decode kernel, whose tiles are 128-row boxes of the same matrix.
 int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail(Q35B_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver.");
@@ -388,6 +391,8 @@ int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, i
   }
   return Q35B_OK;
 }
+
+namespace {
 
 template <int BLOCK_N>
 int launch_tile(q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_scales, const float * g_dev, int m,

@@ -1,0 +1,589 @@
+// Streaming W4A16 decode projection for sm_100a: one persistent launch walks a
+// work list of (projection, 128-row block) tiles; M = 1..8 tokens.
+//
+// Replaces the per-phase matvec loops of the reference's persistent decode
+// kernel (src/kernels/cuda/decode_kernel.cuh:58-84 calling nvfp4_row_dot,
+// src/kernels/cuda/decode_layers.cuh:200-261) for the projections of a step.
+//
+// Data movement (what bounds the kernel): per 256-column K step a tile moves
+//   16 KB of codes   128 rows x 128 B, cp.async.bulk.tensor.2d, 128B swizzle,
+//                    straight from the checkpoint-order [rows, K/2] matrix
+//    2 KB of scales  four 512-byte 128x4 tiles, cp.async.bulk
+// into a shared-memory ring (mbarrier full/empty pairs), so each CTA keeps
+// (stages x 18 KB) in flight regardless of how its consumer warps are doing.
+//
+// Arithmetic (kept off the critical path): each of 8 consumer warps owns 16
+// rows of the tile.  ldmatrix pulls 8 E2M1 codes per lane per register,
+// cvt.rn.f16x2.e2m1x2 (the sm_100a FP4 converter) turns every byte into two
+// exact fp16 values, and mma.sync m16n8k16 forms the 16-element block dot
+// products against fp16 activations; the eight MMA columns are (half h of the
+// 32-code chunk, token m<4), so one MMA pair yields, in each lane, the dot
+// product of exactly the block that lane loaded: no cross-lane data movement.
+// The E4M3 block scale multiplies that block dot in fp32 and accumulates.
+// Activations are converted BF16 -> fp16 per (token, K step) with an exact
+// power-of-two scale taken from that step's amax, by a dedicated warp that runs
+// one projection ahead (double-buffered), so the conversion is never waited on.
+//
+// All waits are bounded; on expiry a code is written to the batch's status word.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <queue>
+#include <vector>
+
+#include "engine.h"
+#include "nvfp4_codec.cuh"
+
+namespace q35b {
+namespace {
+
+constexpr int kTileRows = 128;
+constexpr int kStepBytes = 128;                 // 256 codes per row per K step
+constexpr int kCodesBytes = kTileRows * kStepBytes;
+constexpr int kScaleBytes = 4 * 512;
+constexpr int kStageBytes = kCodesBytes + kScaleBytes;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 activation prep, 8 consumers
+constexpr int kMaxStages = 8;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int kXPad = 8;                        // fp16 elements of padding between tokens in shared memory
+
+enum StatusCode : unsigned { kProducerWait = 11, kPrepWait = 12, kConsumerWait = 13, kConsumerXWait = 14 };
+
+struct alignas(128) GemvItem {
+  CUtensorMap tmap;              // codes [rows, K/2], box 128 rows x 128 bytes, 128B swizzle
+  const uint8_t * scales_tiled;
+  const __nv_bfloat16 * x;       // [m, K]
+  __nv_bfloat16 * y;             // [m, rows]
+  int rows;
+  int k;
+  int k_steps;                   // K / 256
+  float s2;
+};
+
+struct GemvTile {
+  int item;
+  int row_block;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void * p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap * map, uint32_t bar, int x, int y) {
+  asm volatile(
+    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+    "l"(map), "r"(bar), "r"(x), "r"(y)
+    : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void * src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t & r0, uint32_t & r1, uint32_t & r2, uint32_t & r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+// Four bytes of E2M1 pairs -> four fp16x2 registers (low nibble in the low half): exact.
+__device__ __forceinline__ void e2m1x8_to_f16(uint32_t w, uint32_t (&h)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
+}
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile(
+    "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+    : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+    : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Unsigned E4M3 byte (bit 7 clear) in bits [27:20] of `placed` -> fp32 (0x7f = 480, subnormals exact).
+__device__ __forceinline__ float ue4m3_placed_to_f32(uint32_t placed) {
+  return __uint_as_float(placed & 0x07f00000u) * 0x1p120f;
+}
+
+// MT = number of 4-token groups (1 for M <= 4, 2 for M <= 8).
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * __restrict__ tiles,
+                         const int * __restrict__ cta_begin, int m_tokens, const __nv_bfloat16 * x_override,
+                         __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
+                         unsigned int * status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t * ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  __half * xbuf = reinterpret_cast<__half *>(ring + stages * kStageBytes);        // 2 buffers of x_buf_halfs
+  float * xsbuf = reinterpret_cast<float *>(xbuf + 2 * x_buf_halfs);               // 2 buffers of xs_buf_floats (1/scale)
+  uint64_t * bars = reinterpret_cast<uint64_t *>(xsbuf + 2 * xs_buf_floats);
+  // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2]
+  uint64_t * full = bars;
+  uint64_t * empty = bars + kMaxStages;
+  uint64_t * xfull = bars + 2 * kMaxStages;
+  uint64_t * xempty = xfull + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile_begin = cta_begin[blockIdx.x];
+  const int tile_end = cta_begin[blockIdx.x + 1];
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < stages; ++i) {
+      mbar_init(smem_u32(full + i), 1);
+      mbar_init(smem_u32(empty + i), kConsumerWarps);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(xfull + i), 1);
+      mbar_init(smem_u32(xempty + i), kConsumerWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int ti = tile_begin; ti < tile_end && ok; ++ti) {
+        const GemvTile tile = tiles[ti];
+        const GemvItem * item = items + tile.item;
+        const int k_steps = item->k_steps;
+        const uint8_t * sc = item->scales_tiled + static_cast<size_t>(tile.row_block) * k_steps * kScaleBytes;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int stage = it % stages;
+          const uint32_t phase = (it / stages) & 1;
+          if (!mbar_wait(smem_u32(empty + stage), phase ^ 1)) {
+            atomicExch(status, kProducerWait);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(full + stage);
+          uint8_t * dst = ring + stage * kStageBytes;
+          mbar_expect_tx(bar, kStageBytes);
+          tma_load_2d(smem_u32(dst), &item->tmap, bar, ks * kStepBytes, tile.row_block * kTileRows);
+          bulk_load(smem_u32(dst + kCodesBytes), sc + static_cast<size_t>(ks) * kScaleBytes, kScaleBytes, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ activation prep (BF16 -> scaled fp16)
+    int prev_item = -1;
+    uint32_t xi = 0;
+    bool ok = true;
+    for (int ti = tile_begin; ti < tile_end && ok; ++ti) {
+      const int item_index = tiles[ti].item;
+      if (item_index == prev_item) continue;
+      prev_item = item_index;
+      const GemvItem * item = items + item_index;
+      const int buf = xi & 1;
+      if (!mbar_wait(smem_u32(xempty + buf), ((xi >> 1) & 1) ^ 1)) {
+        if (lane == 0) atomicExch(status, kPrepWait);
+        ok = false;
+        break;
+      }
+      const int k = item->k;
+      const int k_steps = item->k_steps;
+      const int xstride = k + kXPad;
+      const __nv_bfloat16 * x = x_override != nullptr ? x_override : item->x;
+      __half * xb = xbuf + buf * x_buf_halfs;
+      float * xs = xsbuf + buf * xs_buf_floats;
+      for (int u = 0; u < m_tokens * k_steps; ++u) {
+        const int token = u / k_steps;
+        const int ks = u - token * k_steps;
+        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(token) * k + ks * 256 + lane * 8));
+        const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+        uint32_t amax_bits = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          amax_bits = max(amax_bits, (r[j] << 16) & 0x7fffffffu);
+          amax_bits = max(amax_bits, r[j] & 0x7fff0000u);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, off));
+        // exact power-of-two scale putting the step's amax in [2^14, 2^15); exponent field clamped to stay normal
+        int e = static_cast<int>(amax_bits >> 23);
+        e = min(max(e, 16), 254);
+        const float scale = __uint_as_float(static_cast<uint32_t>(268 - e) << 23);
+        const float inv_scale = __uint_as_float(static_cast<uint32_t>(e - 14) << 23);
+        uint32_t out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __half2 h = __floats2half2_rn(__uint_as_float(r[j] << 16) * scale, __uint_as_float(r[j] & 0xffff0000u) * scale);
+          out[j] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(xb + static_cast<size_t>(token) * xstride + ks * 256 + lane * 8) =
+          make_uint4(out[0], out[1], out[2], out[3]);
+        if (lane == 0) xs[token * k_steps + ks] = inv_scale;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(xfull + buf));
+      ++xi;
+    }
+  } else {
+    // ------------------------------------------------------------ consumers
+    const int cw = warp - 2;           // 0..7, owns tile rows 16*cw .. 16*cw+15
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    // B-operand role of this lane: MMA column g = (half hB, token mB); it feeds k-slots owned by quad thread t.
+    const int hB = g >> 2;
+    const int mB = g & 3;
+    const bool b_owner = (t >> 1) == hB;
+    // D role: this lane receives block half hD = t >> 1, tokens 2*(t&1), 2*(t&1)+1 for rows g and g+8.
+    const int hD = t >> 1;
+    // ldmatrix row address of this lane: matrix mi = lane >> 3 -> rows 8*(mi&1).., chunk offset mi >> 1
+    const int lm_row = 16 * cw + 8 * ((lane >> 3) & 1) + (lane & 7);
+    const int lm_chunk = lane >> 4;
+    // scale word address pieces: row r -> (r % 32) * 16 + (r / 32) * 4 inside a 512-byte tile
+    const int r0 = 16 * cw + g;
+    const int sc_off0 = (r0 & 31) * 16 + (r0 >> 5) * 4;
+    const int sc_off1 = sc_off0 + 8 * 16;  // row r0 + 8 (same 32-row group)
+
+    uint32_t it = 0;
+    uint32_t xi = 0;
+    int prev_item = -1;
+    int buf = 0;
+    bool ok = true;
+    for (int ti = tile_begin; ti < tile_end && ok; ++ti) {
+      const GemvTile tile = tiles[ti];
+      const GemvItem * item = items + tile.item;
+      if (tile.item != prev_item) {
+        if (prev_item >= 0) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(xempty + buf));
+        }
+        prev_item = tile.item;
+        buf = xi & 1;
+        if (!mbar_wait(smem_u32(xfull + buf), (xi >> 1) & 1)) {
+          if (lane == 0) atomicExch(status, kConsumerXWait);
+          ok = false;
+          break;
+        }
+        ++xi;
+      }
+      const int k = item->k;
+      const int k_steps = item->k_steps;
+      const int xstride = k + kXPad;
+      const __half * xb = xbuf + buf * x_buf_halfs;
+      const float * xs = xsbuf + buf * xs_buf_floats;
+
+      float acc[MT][4];
+#pragma unroll
+      for (int ts = 0; ts < MT; ++ts)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[ts][i] = 0.0f;
+
+      for (int ks = 0; ks < k_steps; ++ks, ++it) {
+        const int stage = it % stages;
+        if (!mbar_wait(smem_u32(full + stage), (it / stages) & 1)) {
+          if (lane == 0) atomicExch(status, kConsumerWait);
+          ok = false;
+          break;
+        }
+        const uint8_t * codes = ring + stage * kStageBytes;
+        const uint8_t * sc = codes + kCodesBytes;
+        const uint32_t codes_addr = smem_u32(codes);
+
+        float sacc[MT][4];
+#pragma unroll
+        for (int ts = 0; ts < MT; ++ts)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sacc[ts][i] = 0.0f;
+
+#pragma unroll
+        for (int pair = 0; pair < 4; ++pair) {
+          uint32_t r[4];
+          {
+            const int ch = 2 * pair + lm_chunk;
+            ldmatrix_x4(codes_addr + lm_row * kStepBytes + ((ch ^ (lm_row & 7)) << 4), r[0], r[1], r[2], r[3]);
+          }
+          // scale words of this pair's 4-block tile: blocks 4*pair .. 4*pair+3 of rows r0 and r0+8
+          const uint32_t w0 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off0);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off1);
+#pragma unroll
+          for (int cq = 0; cq < 2; ++cq) {
+            const int q = 2 * pair + cq;  // 32-code chunk index inside the K step
+            uint32_t a_lo[4], a_hi[4];
+            e2m1x8_to_f16(r[2 * cq], a_lo);      // rows 0..7 of the warp's 16
+            e2m1x8_to_f16(r[2 * cq + 1], a_hi);  // rows 8..15
+            // block 2*cq + hD of the 4-block tile -> byte (2*cq + hD) of the scale words
+            const int sh = 20 - 8 * (2 * cq + hD);
+            const float s0 = ue4m3_placed_to_f32(sh >= 0 ? (w0 << sh) : (w0 >> (-sh)));
+            const float s1 = ue4m3_placed_to_f32(sh >= 0 ? (w1 << sh) : (w1 >> (-sh)));
+#pragma unroll
+            for (int ts = 0; ts < MT; ++ts) {
+              const int token = 4 * ts + mB;
+              uint4 b = make_uint4(0u, 0u, 0u, 0u);
+              if (b_owner && token < m_tokens) {
+                b = *reinterpret_cast<const uint4 *>(xb + static_cast<size_t>(token) * xstride + ks * 256 + 32 * q +
+                                                     16 * hB + 8 * (t & 1));
+              }
+              float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+              mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
+              mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
+              sacc[ts][0] = fmaf(c[0], s0, sacc[ts][0]);
+              sacc[ts][1] = fmaf(c[1], s0, sacc[ts][1]);
+              sacc[ts][2] = fmaf(c[2], s1, sacc[ts][2]);
+              sacc[ts][3] = fmaf(c[3], s1, sacc[ts][3]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empty + stage));
+        // undo the activation scale of this K step (tokens 2*(t&1), +1 of each group)
+#pragma unroll
+        for (int ts = 0; ts < MT; ++ts) {
+          const int tok0 = 4 * ts + 2 * (t & 1);
+          const float i0 = (tok0 < m_tokens) ? xs[tok0 * k_steps + ks] : 0.0f;
+          const float i1 = (tok0 + 1 < m_tokens) ? xs[(tok0 + 1) * k_steps + ks] : 0.0f;
+          acc[ts][0] = fmaf(sacc[ts][0], i0, acc[ts][0]);
+          acc[ts][1] = fmaf(sacc[ts][1], i1, acc[ts][1]);
+          acc[ts][2] = fmaf(sacc[ts][2], i0, acc[ts][2]);
+          acc[ts][3] = fmaf(sacc[ts][3], i1, acc[ts][3]);
+        }
+      }
+      if (!ok) break;
+
+      // combine the two block halves (lanes t and t^2), then lanes t < 2 store tokens 2t, 2t+1
+      __nv_bfloat16 * y = y_override != nullptr ? y_override : item->y;
+      const int rows = item->rows;
+      const float s2 = item->s2;
+      const int row_a = tile.row_block * kTileRows + r0;
+#pragma unroll
+      for (int ts = 0; ts < MT; ++ts) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[ts][i] += __shfl_xor_sync(0xffffffffu, acc[ts][i], 2);
+        if (t < 2) {
+          const int tok0 = 4 * ts + 2 * t;
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            if (tok0 + e < m_tokens) {
+              if (row_a < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a] = __float2bfloat16_rn(acc[ts][e] * s2);
+              if (row_a + 8 < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a + 8] = __float2bfloat16_rn(acc[ts][2 + e] * s2);
+            }
+          }
+        }
+      }
+    }
+    if (ok && prev_item >= 0) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(xempty + buf));
+    }
+  }
+}
+
+constexpr int kSmemBudget = 227 * 1024;
+constexpr int kBarrierBytes = (2 * kMaxStages + 4) * 8;
+
+struct Plan {
+  int stages = 0;
+  int x_buf_halfs = 0;
+  int xs_buf_floats = 0;
+  int smem_bytes = 0;
+};
+
+// Shared-memory plan for a batch with at most max_k columns: two activation buffers, then as many ring stages as fit.
+bool make_plan(int m, int max_k, Plan * p) {
+  const int x_halfs = ((m * (max_k + kXPad) + 7) / 8) * 8;
+  const int xs_floats = ((m * (max_k / 256) + 3) / 4) * 4;
+  const int fixed = 1024 + 2 * x_halfs * 2 + 2 * xs_floats * 4 + kBarrierBytes;
+  const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
+  if (stages < 3) return false;
+  p->stages = stages;
+  p->x_buf_halfs = x_halfs;
+  p->xs_buf_floats = xs_floats;
+  p->smem_bytes = fixed + stages * kStageBytes;
+  return true;
+}
+
+}  // namespace
+}  // namespace q35b
+
+using namespace q35b;
+
+struct q35b_gemv_batch {
+  int count = 0;
+  int m = 0;
+  int grid = 0;
+  int device = 0;
+  Plan plan;
+  void * dev_base = nullptr;
+  GemvItem * items = nullptr;
+  GemvTile * tiles = nullptr;
+  int * cta_begin = nullptr;
+  unsigned int * status = nullptr;
+  size_t bytes_per_run = 0;
+};
+
+namespace q35b {
+
+bool gemv_stream_eligible(const q35b_weight * w, int m) {
+  if (w == nullptr || w->rows <= 0 || (w->k % 256) != 0 || w->negative_scales) return false;
+  Plan p;
+  return make_plan(m, w->k, &p);
+}
+
+int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out) {
+  if (items == nullptr || out == nullptr || count <= 0) return fail(Q35B_ERR_ARGUMENT, "Invalid NVFP4 projection work list.");
+  if (m < 1 || m > 8) return fail(Q35B_ERR_SHAPE, "NVFP4 decode projection supports 1..8 tokens.");
+  *out = nullptr;
+  int max_k = 0;
+  for (int i = 0; i < count; ++i) {
+    const q35b_weight * w = items[i].weight;
+    if (w == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 projection work list holds a null weight.");
+    if ((w->k % 256) != 0) return fail(Q35B_ERR_SHAPE, "The streaming NVFP4 projection needs cols to be a multiple of 256.");
+    if (w->negative_scales) return fail(Q35B_ERR_FORMAT, "The streaming NVFP4 projection needs unsigned E4M3 block scales.");
+    max_k = std::max(max_k, w->k);
+  }
+  auto * b = new q35b_gemv_batch();
+  b->count = count;
+  b->m = m;
+  if (!make_plan(m, max_k, &b->plan)) {
+    delete b;
+    return fail(Q35B_ERR_SHAPE, "Activations of the NVFP4 projection work list do not fit in shared memory.");
+  }
+  if (cudaGetDevice(&b->device) != cudaSuccess) {
+    delete b;
+    return fail_cuda(cudaGetLastError(), "cudaGetDevice");
+  }
+  const int grid_max = sm_count();
+
+  // Tiles, heaviest first, dealt to the least loaded CTA; each CTA then walks its tiles grouped by projection.
+  struct T { int item, rb, cost; };
+  std::vector<T> all;
+  std::vector<GemvItem> h_items(count);
+  for (int i = 0; i < count; ++i) {
+    const q35b_weight * w = items[i].weight;
+    GemvItem & it = h_items[i];
+    if (const int st = make_code_map(&it.tmap, w->codes, std::max(w->rows, 1), w->k / 2, kTileRows)) {
+      delete b;
+      return st;
+    }
+    it.scales_tiled = w->scales_tiled;
+    it.x = static_cast<const __nv_bfloat16 *>(items[i].x_bf16);
+    it.y = static_cast<__nv_bfloat16 *>(items[i].y_bf16);
+    it.rows = w->rows;
+    it.k = w->k;
+    it.k_steps = w->k / 256;
+    it.s2 = w->s2;
+    for (int rb = 0; rb < (w->rows + kTileRows - 1) / kTileRows; ++rb) all.push_back({i, rb, it.k_steps});
+    b->bytes_per_run += w->codes_bytes + w->scales_bytes;
+  }
+  const int grid = std::max(1, std::min<int>(grid_max, static_cast<int>(all.size())));
+  std::stable_sort(all.begin(), all.end(), [](const T & a, const T & c) { return a.cost > c.cost; });
+  using Load = std::pair<long, int>;
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int c = 0; c < grid; ++c) heap.push({0, c});
+  std::vector<std::vector<T>> per_cta(grid);
+  for (const T & tl : all) {
+    Load l = heap.top();
+    heap.pop();
+    per_cta[l.second].push_back(tl);
+    heap.push({l.first + tl.cost + 1, l.second});
+  }
+  std::vector<GemvTile> h_tiles;
+  std::vector<int> h_begin(grid + 1, 0);
+  for (int c = 0; c < grid; ++c) {
+    std::stable_sort(per_cta[c].begin(), per_cta[c].end(),
+                     [](const T & a, const T & d) { return a.item != d.item ? a.item < d.item : a.rb < d.rb; });
+    h_begin[c] = static_cast<int>(h_tiles.size());
+    for (const T & tl : per_cta[c]) h_tiles.push_back({tl.item, tl.rb});
+  }
+  h_begin[grid] = static_cast<int>(h_tiles.size());
+  b->grid = grid;
+
+  const size_t o_tiles = sizeof(GemvItem) * count;
+  const size_t o_begin = (o_tiles + sizeof(GemvTile) * h_tiles.size() + 15) / 16 * 16;
+  const size_t o_status = (o_begin + sizeof(int) * (grid + 1) + 15) / 16 * 16;
+  const size_t total = o_status + 16;
+  cudaError_t e = cudaMalloc(&b->dev_base, total);
+  if (e != cudaSuccess) {
+    delete b;
+    return fail_cuda(e, "cudaMalloc(projection work list)");
+  }
+  auto * base = static_cast<uint8_t *>(b->dev_base);
+  b->items = reinterpret_cast<GemvItem *>(base);
+  b->tiles = reinterpret_cast<GemvTile *>(base + o_tiles);
+  b->cta_begin = reinterpret_cast<int *>(base + o_begin);
+  b->status = reinterpret_cast<unsigned int *>(base + o_status);
+  e = cudaMemcpy(b->items, h_items.data(), sizeof(GemvItem) * count, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(b->tiles, h_tiles.data(), sizeof(GemvTile) * h_tiles.size(), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(b->cta_begin, h_begin.data(), sizeof(int) * (grid + 1), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemset(b->status, 0, 16);
+  if (e == cudaSuccess) {
+    e = cudaFuncSetAttribute(gemv_w4a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+  }
+  if (e == cudaSuccess) {
+    e = cudaFuncSetAttribute(gemv_w4a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+  }
+  if (e != cudaSuccess) {
+    cudaFree(b->dev_base);
+    delete b;
+    return fail_cuda(e, "uploading the projection work list");
+  }
+  *out = b;
+  return Q35B_OK;
+}
+
+int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void * y_override, cudaStream_t s) {
+  if (b == nullptr) return fail(Q35B_ERR_ARGUMENT, "Null NVFP4 projection work list.");
+  const auto * xo = static_cast<const __nv_bfloat16 *>(x_override);
+  auto * yo = static_cast<__nv_bfloat16 *>(y_override);
+  if (b->m <= 4) {
+    gemv_w4a16_stream_kernel<1><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
+      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->status);
+  } else {
+    gemv_w4a16_stream_kernel<2><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
+      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->status);
+  }
+  count_launch();
+  Q35B_CUDA_TRY(cudaGetLastError(), "gemv_w4a16_stream_kernel launch");
+  return Q35B_OK;
+}
+
+void gemv_batch_free(q35b_gemv_batch * b) {
+  if (b == nullptr) return;
+  if (b->dev_base != nullptr) cudaFree(b->dev_base);
+  delete b;
+}
+
+int gemv_batch_read_status(const q35b_gemv_batch * b, unsigned int * out) {
+  if (b == nullptr || out == nullptr) return fail(Q35B_ERR_ARGUMENT, "Null NVFP4 projection work list.");
+  Q35B_CUDA_TRY(cudaMemcpy(out, b->status, sizeof(unsigned int), cudaMemcpyDeviceToHost), "cudaMemcpy(work list status)");
+  return Q35B_OK;
+}
+
+size_t gemv_batch_bytes(const q35b_gemv_batch * b) { return b ? b->bytes_per_run : 0; }
+
+}  // namespace q35b

@@ -52,6 +52,16 @@ def lib() -> C.CDLL:
     L.q35b_gemv_w4a16_bf16.argtypes = [vp, vp, i, vp, i, vp]
     L.q35b_gemv_w4a16_f32.restype = i
     L.q35b_gemv_w4a16_f32.argtypes = [vp, vp, f, vp, i, vp]
+    L.q35b_gemv_batch_create.restype = i
+    L.q35b_gemv_batch_create.argtypes = [vp, i, i, C.POINTER(vp)]
+    L.q35b_gemv_batch_run.restype = i
+    L.q35b_gemv_batch_run.argtypes = [vp, vp]
+    L.q35b_gemv_batch_destroy.restype = None
+    L.q35b_gemv_batch_destroy.argtypes = [vp]
+    L.q35b_gemv_batch_status.restype = i
+    L.q35b_gemv_batch_status.argtypes = [vp, C.POINTER(C.c_uint)]
+    L.q35b_gemv_batch_stream_bytes.restype = sz
+    L.q35b_gemv_batch_stream_bytes.argtypes = [vp]
     L.q35b_act_codes_bytes.restype = sz
     L.q35b_act_codes_bytes.argtypes = [i, i]
     L.q35b_act_scales_bytes.restype = sz
@@ -189,6 +199,49 @@ def gemv_w4a16_f32(weight: Nvfp4Weight, x, input_scale: float = 1.0, out=None, k
     _check(lib().q35b_gemv_w4a16_f32(weight.handle, x.data_ptr(), input_scale, out.data_ptr(), kernel,
                                      _stream_ptr(torch)))
     return out
+
+
+class _GemvItem(C.Structure):
+    _fields_ = [("weight", C.c_void_p), ("x_bf16", C.c_void_p), ("y_bf16", C.c_void_p)]
+
+
+class GemvBatch:
+    """A prepared work list of independent decode projections run by one persistent launch
+    (q35b_gemv_batch_* in include/q35b_nvfp4.h).  items: sequence of (Nvfp4Weight, x [m,K] bf16, y [m,rows] bf16);
+    the tensors must stay alive and in place for the life of the batch."""
+
+    def __init__(self, items, m: int):
+        torch = _torch()
+        self._keep = list(items)
+        arr = (_GemvItem * len(self._keep))()
+        for j, (w, x, y) in enumerate(self._keep):
+            assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and tuple(x.shape) == (m, w.k)
+            assert y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and tuple(y.shape) == (m, w.rows)
+            arr[j] = _GemvItem(w.handle.value, x.data_ptr(), y.data_ptr())
+        h = C.c_void_p()
+        _check(lib().q35b_gemv_batch_create(arr, len(self._keep), m, C.byref(h)))
+        self._h = h
+        self.m = m
+        self.stream_bytes = int(lib().q35b_gemv_batch_stream_bytes(h))
+
+    def run(self) -> None:
+        _check(lib().q35b_gemv_batch_run(self._h, _stream_ptr(_torch())))
+
+    def status(self) -> int:
+        out = C.c_uint(0)
+        _check(lib().q35b_gemv_batch_status(self._h, C.byref(out)))
+        return int(out.value)
+
+    def close(self) -> None:
+        if self._h is not None and self._h.value:
+            lib().q35b_gemv_batch_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 _workspaces: dict = {}
