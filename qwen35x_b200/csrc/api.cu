@@ -222,6 +222,9 @@ int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void
     }
     if (m < 1 || m > 8) return fail(Q35B_ERR_SHAPE, "NVFP4 decode projection supports 1..8 tokens.");
     if (w->rows == 0) return Q35B_OK;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) {
+      return fail(Q35B_ERR_ARGUMENT, "Activations of the streaming NVFP4 projection must be 16-byte aligned.");
+    }
     auto * wm = const_cast<q35b_weight *>(w);
     if (wm->stream_batch[m] == nullptr) {
       // first use with this token count: build (and upload) the single-projection work list

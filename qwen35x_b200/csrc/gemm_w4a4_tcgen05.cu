@@ -189,7 +189,7 @@ gemm_w4a4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   using C = Cfg<BLOCK_N>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128B-swizzled operand tiles.
-  uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t * smem_a = smem;
   uint8_t * smem_b = smem_a + C::kStages * C::kABytes;
   uint8_t * smem_sfa = smem_b + C::kStages * C::kBBytes;

@@ -12,8 +12,9 @@
 // into a shared-memory ring (mbarrier full/empty pairs), so each CTA keeps
 // (stages x 18 KB) in flight regardless of how its consumer warps are doing.
 //
-// Arithmetic (kept off the critical path): each of 8 consumer warps owns 16
-// rows of the tile.  ldmatrix pulls 8 E2M1 codes per lane per register,
+// Arithmetic (kept off the critical path): 16 consumer warps; a pair of warps
+// owns 16 rows of the tile, each taking half of the K step (their partial sums
+// meet in shared memory at the end of the tile).  ldmatrix pulls 8 E2M1 codes per lane per register,
 // cvt.rn.f16x2.e2m1x2 (the sm_100a FP4 converter) turns every byte into two
 // exact fp16 values, and mma.sync m16n8k16 forms the 16-element block dot
 // products against fp16 activations; the eight MMA columns are (half h of the
@@ -43,9 +44,12 @@ constexpr int kStepBytes = 128;                 // 256 codes per row per K step
 constexpr int kCodesBytes = kTileRows * kStepBytes;
 constexpr int kScaleBytes = 4 * 512;
 constexpr int kStageBytes = kCodesBytes + kScaleBytes;
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 activation prep, 8 consumers
+constexpr int kRowGroups = 8;                   // 16-row groups per tile
+constexpr int kConsumerWarps = 16;              // each row group is shared by two warps that split the K step
+constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 activation prep, 16 consumers
+constexpr int kMaxTilesInSmem = 64;             // tile descriptors staged per CTA
 constexpr int kMaxStages = 8;
+constexpr int kMaxRawDepth = 4;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kXPad = 8;                        // fp16 elements of padding between tokens in shared memory
 
@@ -62,9 +66,19 @@ struct alignas(128) GemvItem {
   float s2;
 };
 
-struct GemvTile {
+// Everything a CTA needs to know about one tile, staged in shared memory at kernel start so that no role chases
+// pointers through global memory at a tile boundary.
+struct alignas(16) GemvTile {
   int item;
   int row_block;
+  int k;
+  int k_steps;
+  int rows;
+  float s2;
+  const uint8_t * scales;        // tiled scales of this row block
+  const uint8_t * codes;         // first code byte of this row block
+  const __nv_bfloat16 * x;
+  __nv_bfloat16 * y;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -122,8 +136,16 @@ __device__ __forceinline__ void e2m1x8_to_f16(uint32_t w, uint32_t (&h)[4]) {
       : "r"(w));
 }
 
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                        uint32_t b1) {
+// d = a * b (+ c): fp16 operands, fp32 accumulate.
+__device__ __forceinline__ void mma_f16_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+  asm volatile(
+    "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+    : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+    : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+__device__ __forceinline__ void mma_f16_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1) {
   asm volatile(
     "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -141,22 +163,30 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * __restrict__ tiles,
                          const int * __restrict__ cta_begin, int m_tokens, const __nv_bfloat16 * x_override,
                          __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
-                         unsigned int * status) {
+                         int x_raw_bytes, int x_raw_depth, unsigned int * status) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t * ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // 1024-byte alignment for the swizzled code tiles; pointer arithmetic on the __shared__ array (rather than an
+  // integer round trip) keeps every later access a shared-memory access for the compiler.
+  uint8_t * ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __half * xbuf = reinterpret_cast<__half *>(ring + stages * kStageBytes);        // 2 buffers of x_buf_halfs
   float * xsbuf = reinterpret_cast<float *>(xbuf + 2 * x_buf_halfs);               // 2 buffers of xs_buf_floats (1/scale)
-  uint64_t * bars = reinterpret_cast<uint64_t *>(xsbuf + 2 * xs_buf_floats);
-  // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2]
+  float * red = xsbuf + 2 * xs_buf_floats;                                         // 2 x [8 row groups][32 lanes][4*MT]
+  GemvTile * stile = reinterpret_cast<GemvTile *>(red + 2 * kRowGroups * 32 * 4 * MT);
+  uint8_t * xraw = reinterpret_cast<uint8_t *>(stile + kMaxTilesInSmem);           // x_raw_depth buffers of x_raw_bytes
+  uint64_t * bars = reinterpret_cast<uint64_t *>(xraw + static_cast<size_t>(x_raw_depth) * x_raw_bytes);
+  // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2], red_full[2], red_free[2], xraw_full[kMaxRawDepth]
   uint64_t * full = bars;
   uint64_t * empty = bars + kMaxStages;
   uint64_t * xfull = bars + 2 * kMaxStages;
   uint64_t * xempty = xfull + 2;
+  uint64_t * red_full = xempty + 2;
+  uint64_t * red_free = red_full + 2;
+  uint64_t * xraw_full = red_free + 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tile_begin = cta_begin[blockIdx.x];
-  const int tile_end = cta_begin[blockIdx.x + 1];
+  const int n_tiles = cta_begin[blockIdx.x + 1] - tile_begin;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < stages; ++i) {
@@ -166,21 +196,34 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(xfull + i), 1);
       mbar_init(smem_u32(xempty + i), kConsumerWarps);
+      mbar_init(smem_u32(red_full + i), kRowGroups);
+      mbar_init(smem_u32(red_free + i), kRowGroups);
     }
+    for (int i = 0; i < x_raw_depth; ++i) mbar_init(smem_u32(xraw_full + i), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // stage this CTA's tile descriptors
+  {
+    const int n_stage = min(n_tiles, kMaxTilesInSmem);
+    constexpr int kWords = sizeof(GemvTile) / 16;
+    const uint4 * src = reinterpret_cast<const uint4 *>(tiles + tile_begin);
+    uint4 * dst = reinterpret_cast<uint4 *>(stile);
+    for (int i = threadIdx.x; i < n_stage * kWords; i += kThreads) dst[i] = __ldg(src + i);
+  }
   __syncthreads();
+  auto tile_at = [&](int i) -> const GemvTile * { return i < kMaxTilesInSmem ? stile + i : tiles + tile_begin + i; };
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int ti = tile_begin; ti < tile_end && ok; ++ti) {
-        const GemvTile tile = tiles[ti];
-        const GemvItem * item = items + tile.item;
-        const int k_steps = item->k_steps;
-        const uint8_t * sc = item->scales_tiled + static_cast<size_t>(tile.row_block) * k_steps * kScaleBytes;
+      for (int ti = 0; ti < n_tiles && ok; ++ti) {
+        const GemvTile * tile = tile_at(ti);
+        const CUtensorMap * tmap = &items[tile->item].tmap;
+        const int k_steps = tile->k_steps;
+        const uint8_t * sc = tile->scales;
+        const int row0 = tile->row_block * kTileRows;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int stage = it % stages;
           const uint32_t phase = (it / stages) & 1;
@@ -192,37 +235,55 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           const uint32_t bar = smem_u32(full + stage);
           uint8_t * dst = ring + stage * kStageBytes;
           mbar_expect_tx(bar, kStageBytes);
-          tma_load_2d(smem_u32(dst), &item->tmap, bar, ks * kStepBytes, tile.row_block * kTileRows);
+          tma_load_2d(smem_u32(dst), tmap, bar, ks * kStepBytes, row0);
           bulk_load(smem_u32(dst + kCodesBytes), sc + static_cast<size_t>(ks) * kScaleBytes, kScaleBytes, bar);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ activation prep (BF16 -> scaled fp16)
-    int prev_item = -1;
+    // Raw BF16 activations of the next projections are bulk-copied into a small ring ahead of time (so no global
+    // latency is ever waited on here), then converted into one of the two fp16 buffers the consumers read.
+    auto next_run = [&](int ti, int prev) {  // first tile index >= ti whose projection differs from `prev`
+      while (ti < n_tiles && tile_at(ti)->item == prev) ++ti;
+      return ti;
+    };
+    int issue_ti = next_run(0, -1);
+    uint32_t issued = 0;
+    int proc_ti = issue_ti;
     uint32_t xi = 0;
-    bool ok = true;
-    for (int ti = tile_begin; ti < tile_end && ok; ++ti) {
-      const int item_index = tiles[ti].item;
-      if (item_index == prev_item) continue;
-      prev_item = item_index;
-      const GemvItem * item = items + item_index;
+    while (proc_ti < n_tiles) {
+      // keep up to x_raw_depth raw copies in flight
+      while (issue_ti < n_tiles && issued < xi + static_cast<uint32_t>(x_raw_depth)) {
+        const GemvTile * tl = tile_at(issue_ti);
+        if (lane == 0) {
+          const uint32_t rb = issued % x_raw_depth;
+          const uint32_t bytes = static_cast<uint32_t>(m_tokens) * tl->k * 2u;
+          const __nv_bfloat16 * x = x_override != nullptr ? x_override : tl->x;
+          mbar_expect_tx(smem_u32(xraw_full + rb), bytes);
+          bulk_load(smem_u32(xraw + static_cast<size_t>(rb) * x_raw_bytes), x, bytes, smem_u32(xraw_full + rb));
+        }
+        ++issued;
+        issue_ti = next_run(issue_ti + 1, tl->item);
+      }
+      const GemvTile * tile = tile_at(proc_ti);
       const int buf = xi & 1;
-      if (!mbar_wait(smem_u32(xempty + buf), ((xi >> 1) & 1) ^ 1)) {
+      const uint32_t rb = xi % x_raw_depth;
+      if (!mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1) ||
+          !mbar_wait(smem_u32(xempty + buf), ((xi >> 1) & 1) ^ 1)) {
         if (lane == 0) atomicExch(status, kPrepWait);
-        ok = false;
         break;
       }
-      const int k = item->k;
-      const int k_steps = item->k_steps;
+      const int k = tile->k;
+      const int k_steps = tile->k_steps;
       const int xstride = k + kXPad;
-      const __nv_bfloat16 * x = x_override != nullptr ? x_override : item->x;
+      const __nv_bfloat16 * x = reinterpret_cast<const __nv_bfloat16 *>(xraw + static_cast<size_t>(rb) * x_raw_bytes);
       __half * xb = xbuf + buf * x_buf_halfs;
       float * xs = xsbuf + buf * xs_buf_floats;
       for (int u = 0; u < m_tokens * k_steps; ++u) {
         const int token = u / k_steps;
         const int ks = u - token * k_steps;
-        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(token) * k + ks * 256 + lane * 8));
+        const uint4 q = *reinterpret_cast<const uint4 *>(x + static_cast<size_t>(token) * k + ks * 256 + lane * 8);
         const uint32_t r[4] = {q.x, q.y, q.z, q.w};
         uint32_t amax_bits = 0;
 #pragma unroll
@@ -250,10 +311,13 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(xfull + buf));
       ++xi;
+      proc_ti = next_run(proc_ti + 1, tile->item);
     }
   } else {
     // ------------------------------------------------------------ consumers
-    const int cw = warp - 2;           // 0..7, owns tile rows 16*cw .. 16*cw+15
+    const int cw = warp - 2;           // 0..15
+    const int rg = cw & 7;             // row group: tile rows 16*rg .. 16*rg+15
+    const int kh = cw >> 3;            // which half of every K step (chunk pairs 2*kh, 2*kh+1)
     const int g = lane >> 2;
     const int t = lane & 3;
     // B-operand role of this lane: MMA column g = (half hB, token mB); it feeds k-slots owned by quad thread t.
@@ -263,27 +327,29 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     // D role: this lane receives block half hD = t >> 1, tokens 2*(t&1), 2*(t&1)+1 for rows g and g+8.
     const int hD = t >> 1;
     // ldmatrix row address of this lane: matrix mi = lane >> 3 -> rows 8*(mi&1).., chunk offset mi >> 1
-    const int lm_row = 16 * cw + 8 * ((lane >> 3) & 1) + (lane & 7);
+    const int lm_row = 16 * rg + 8 * ((lane >> 3) & 1) + (lane & 7);
     const int lm_chunk = lane >> 4;
+    const uint32_t lm_row_off = lm_row * kStepBytes;
+    const int lm_xor = lm_row & 7;
     // scale word address pieces: row r -> (r % 32) * 16 + (r / 32) * 4 inside a 512-byte tile
-    const int r0 = 16 * cw + g;
+    const int r0 = 16 * rg + g;
     const int sc_off0 = (r0 & 31) * 16 + (r0 >> 5) * 4;
     const int sc_off1 = sc_off0 + 8 * 16;  // row r0 + 8 (same 32-row group)
+    const int x_lane_off = 16 * hB + 8 * (t & 1);
 
     uint32_t it = 0;
     uint32_t xi = 0;
     int prev_item = -1;
     int buf = 0;
     bool ok = true;
-    for (int ti = tile_begin; ti < tile_end && ok; ++ti) {
-      const GemvTile tile = tiles[ti];
-      const GemvItem * item = items + tile.item;
-      if (tile.item != prev_item) {
+    for (int ti = 0; ti < n_tiles && ok; ++ti) {
+      const GemvTile * tile = tile_at(ti);
+      if (tile->item != prev_item) {
         if (prev_item >= 0) {
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(xempty + buf));
         }
-        prev_item = tile.item;
+        prev_item = tile->item;
         buf = xi & 1;
         if (!mbar_wait(smem_u32(xfull + buf), (xi >> 1) & 1)) {
           if (lane == 0) atomicExch(status, kConsumerXWait);
@@ -292,9 +358,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         }
         ++xi;
       }
-      const int k = item->k;
-      const int k_steps = item->k_steps;
-      const int xstride = k + kXPad;
+      const int k_steps = tile->k_steps;
+      const int xstride = tile->k + kXPad;
       const __half * xb = xbuf + buf * x_buf_halfs;
       const float * xs = xsbuf + buf * xs_buf_floats;
 
@@ -313,7 +378,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         }
         const uint8_t * codes = ring + stage * kStageBytes;
         const uint8_t * sc = codes + kCodesBytes;
-        const uint32_t codes_addr = smem_u32(codes);
+        const uint32_t codes_addr = smem_u32(codes) + lm_row_off;
 
         float sacc[MT][4];
 #pragma unroll
@@ -322,12 +387,10 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           for (int i = 0; i < 4; ++i) sacc[ts][i] = 0.0f;
 
 #pragma unroll
-        for (int pair = 0; pair < 4; ++pair) {
+        for (int pp = 0; pp < 2; ++pp) {
+          const int pair = 2 * kh + pp;
           uint32_t r[4];
-          {
-            const int ch = 2 * pair + lm_chunk;
-            ldmatrix_x4(codes_addr + lm_row * kStepBytes + ((ch ^ (lm_row & 7)) << 4), r[0], r[1], r[2], r[3]);
-          }
+          ldmatrix_x4(codes_addr + (((2 * pair + lm_chunk) ^ lm_xor) << 4), r[0], r[1], r[2], r[3]);
           // scale words of this pair's 4-block tile: blocks 4*pair .. 4*pair+3 of rows r0 and r0+8
           const uint32_t w0 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off0);
           const uint32_t w1 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off1);
@@ -346,12 +409,11 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
               const int token = 4 * ts + mB;
               uint4 b = make_uint4(0u, 0u, 0u, 0u);
               if (b_owner && token < m_tokens) {
-                b = *reinterpret_cast<const uint4 *>(xb + static_cast<size_t>(token) * xstride + ks * 256 + 32 * q +
-                                                     16 * hB + 8 * (t & 1));
+                b = *reinterpret_cast<const uint4 *>(xb + static_cast<size_t>(token) * xstride + ks * 256 + 32 * q + x_lane_off);
               }
-              float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-              mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
-              mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
+              float c[4];
+              mma_f16_zero(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
+              mma_f16_acc(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
               sacc[ts][0] = fmaf(c[0], s0, sacc[ts][0]);
               sacc[ts][1] = fmaf(c[1], s0, sacc[ts][1]);
               sacc[ts][2] = fmaf(c[2], s1, sacc[ts][2]);
@@ -375,22 +437,54 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       }
       if (!ok) break;
 
-      // combine the two block halves (lanes t and t^2), then lanes t < 2 store tokens 2t, 2t+1
-      __nv_bfloat16 * y = y_override != nullptr ? y_override : item->y;
-      const int rows = item->rows;
-      const float s2 = item->s2;
-      const int row_a = tile.row_block * kTileRows + r0;
+      // Meet the partner warp's half-K sums in shared memory (double-buffered by tile parity): the kh = 1 warp
+      // writes, the kh = 0 warp adds, combines the two block halves (lanes t and t^2) and stores.
+      const int rb = ti & 1;
+      const uint32_t rphase = (ti >> 1) & 1;
+      float * slot = red + ((rb * kRowGroups + rg) * 32 + lane) * 4 * MT;
+      if (kh == 1) {
+        if (!mbar_wait(smem_u32(red_free + rb), rphase ^ 1)) {
+          if (lane == 0) atomicExch(status, kConsumerWait);
+          ok = false;
+          break;
+        }
 #pragma unroll
-      for (int ts = 0; ts < MT; ++ts) {
+        for (int ts = 0; ts < MT; ++ts)
+          *reinterpret_cast<float4 *>(slot + 4 * ts) = make_float4(acc[ts][0], acc[ts][1], acc[ts][2], acc[ts][3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(red_full + rb));
+      } else {
+        if (!mbar_wait(smem_u32(red_full + rb), rphase)) {
+          if (lane == 0) atomicExch(status, kConsumerWait);
+          ok = false;
+          break;
+        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[ts][i] += __shfl_xor_sync(0xffffffffu, acc[ts][i], 2);
-        if (t < 2) {
-          const int tok0 = 4 * ts + 2 * t;
+        for (int ts = 0; ts < MT; ++ts) {
+          const float4 o = *reinterpret_cast<const float4 *>(slot + 4 * ts);
+          acc[ts][0] += o.x;
+          acc[ts][1] += o.y;
+          acc[ts][2] += o.z;
+          acc[ts][3] += o.w;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(red_free + rb));
+        __nv_bfloat16 * y = y_override != nullptr ? y_override : tile->y;
+        const int rows = tile->rows;
+        const float s2 = tile->s2;
+        const int row_a = tile->row_block * kTileRows + r0;
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            if (tok0 + e < m_tokens) {
-              if (row_a < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a] = __float2bfloat16_rn(acc[ts][e] * s2);
-              if (row_a + 8 < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a + 8] = __float2bfloat16_rn(acc[ts][2 + e] * s2);
+        for (int ts = 0; ts < MT; ++ts) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[ts][i] += __shfl_xor_sync(0xffffffffu, acc[ts][i], 2);
+          if (t < 2) {
+            const int tok0 = 4 * ts + 2 * t;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              if (tok0 + e < m_tokens) {
+                if (row_a < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a] = __float2bfloat16_rn(acc[ts][e] * s2);
+                if (row_a + 8 < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a + 8] = __float2bfloat16_rn(acc[ts][2 + e] * s2);
+              }
             }
           }
         }
@@ -404,26 +498,36 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
 }
 
 constexpr int kSmemBudget = 227 * 1024;
-constexpr int kBarrierBytes = (2 * kMaxStages + 4) * 8;
+constexpr int kBarrierBytes = (2 * kMaxStages + 8 + kMaxRawDepth) * 8;
 
 struct Plan {
   int stages = 0;
   int x_buf_halfs = 0;
   int xs_buf_floats = 0;
+  int x_raw_bytes = 0;
+  int x_raw_depth = 0;
   int smem_bytes = 0;
 };
 
 // Shared-memory plan for a batch with at most max_k columns: two activation buffers, then as many ring stages as fit.
 bool make_plan(int m, int max_k, Plan * p) {
+  const int mt = m <= 4 ? 1 : 2;
   const int x_halfs = ((m * (max_k + kXPad) + 7) / 8) * 8;
   const int xs_floats = ((m * (max_k / 256) + 3) / 4) * 4;
-  const int fixed = 1024 + 2 * x_halfs * 2 + 2 * xs_floats * 4 + kBarrierBytes;
-  const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
+  const int fixed = 1024 + 2 * x_halfs * 2 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 +
+                    kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
+  const int raw_bytes = ((m * max_k * 2 + 127) / 128) * 128;
+  // raw-activation ring: as deep as fits while leaving at least 4 ring stages (3 at the very least)
+  int depth = kMaxRawDepth;
+  while (depth > 1 && (kSmemBudget - fixed - depth * raw_bytes) / kStageBytes < 4) --depth;
+  const int stages = std::min(kMaxStages, (kSmemBudget - fixed - depth * raw_bytes) / kStageBytes);
   if (stages < 3) return false;
   p->stages = stages;
   p->x_buf_halfs = x_halfs;
   p->xs_buf_floats = xs_floats;
-  p->smem_bytes = fixed + stages * kStageBytes;
+  p->x_raw_bytes = raw_bytes;
+  p->x_raw_depth = depth;
+  p->smem_bytes = fixed + depth * raw_bytes + stages * kStageBytes;
   return true;
 }
 
@@ -464,6 +568,9 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
     if (w == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 projection work list holds a null weight.");
     if ((w->k % 256) != 0) return fail(Q35B_ERR_SHAPE, "The streaming NVFP4 projection needs cols to be a multiple of 256.");
     if (w->negative_scales) return fail(Q35B_ERR_FORMAT, "The streaming NVFP4 projection needs unsigned E4M3 block scales.");
+    if ((reinterpret_cast<uintptr_t>(items[i].x_bf16) & 15u) != 0) {
+      return fail(Q35B_ERR_ARGUMENT, "Activations of the NVFP4 projection work list must be 16-byte aligned.");
+    }
     max_k = std::max(max_k, w->k);
   }
   auto * b = new q35b_gemv_batch();
@@ -480,8 +587,7 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
   const int grid_max = sm_count();
 
   // Tiles, heaviest first, dealt to the least loaded CTA; each CTA then walks its tiles grouped by projection.
-  struct T { int item, rb, cost; };
-  std::vector<T> all;
+  std::vector<GemvTile> all;
   std::vector<GemvItem> h_items(count);
   for (int i = 0; i < count; ++i) {
     const q35b_weight * w = items[i].weight;
@@ -497,28 +603,42 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
     it.k = w->k;
     it.k_steps = w->k / 256;
     it.s2 = w->s2;
-    for (int rb = 0; rb < (w->rows + kTileRows - 1) / kTileRows; ++rb) all.push_back({i, rb, it.k_steps});
+    for (int rb = 0; rb < (w->rows + kTileRows - 1) / kTileRows; ++rb) {
+      GemvTile tl;
+      tl.item = i;
+      tl.row_block = rb;
+      tl.k = w->k;
+      tl.k_steps = it.k_steps;
+      tl.rows = w->rows;
+      tl.s2 = w->s2;
+      tl.scales = w->scales_tiled + static_cast<size_t>(rb) * it.k_steps * kScaleBytes;
+      tl.codes = w->codes + static_cast<size_t>(rb) * kTileRows * (w->k / 2);
+      tl.x = it.x;
+      tl.y = it.y;
+      all.push_back(tl);
+    }
     b->bytes_per_run += w->codes_bytes + w->scales_bytes;
   }
   const int grid = std::max(1, std::min<int>(grid_max, static_cast<int>(all.size())));
-  std::stable_sort(all.begin(), all.end(), [](const T & a, const T & c) { return a.cost > c.cost; });
+  std::stable_sort(all.begin(), all.end(), [](const GemvTile & a, const GemvTile & c) { return a.k_steps > c.k_steps; });
   using Load = std::pair<long, int>;
   std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
   for (int c = 0; c < grid; ++c) heap.push({0, c});
-  std::vector<std::vector<T>> per_cta(grid);
-  for (const T & tl : all) {
+  std::vector<std::vector<GemvTile>> per_cta(grid);
+  for (const GemvTile & tl : all) {
     Load l = heap.top();
     heap.pop();
     per_cta[l.second].push_back(tl);
-    heap.push({l.first + tl.cost + 1, l.second});
+    heap.push({l.first + tl.k_steps + 1, l.second});
   }
   std::vector<GemvTile> h_tiles;
   std::vector<int> h_begin(grid + 1, 0);
   for (int c = 0; c < grid; ++c) {
-    std::stable_sort(per_cta[c].begin(), per_cta[c].end(),
-                     [](const T & a, const T & d) { return a.item != d.item ? a.item < d.item : a.rb < d.rb; });
+    std::stable_sort(per_cta[c].begin(), per_cta[c].end(), [](const GemvTile & a, const GemvTile & d) {
+      return a.item != d.item ? a.item < d.item : a.row_block < d.row_block;
+    });
     h_begin[c] = static_cast<int>(h_tiles.size());
-    for (const T & tl : per_cta[c]) h_tiles.push_back({tl.item, tl.rb});
+    for (const GemvTile & tl : per_cta[c]) h_tiles.push_back(tl);
   }
   h_begin[grid] = static_cast<int>(h_tiles.size());
   b->grid = grid;
@@ -562,10 +682,12 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   auto * yo = static_cast<__nv_bfloat16 *>(y_override);
   if (b->m <= 4) {
     gemv_w4a16_stream_kernel<1><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
-      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->status);
+      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
+      b->plan.x_raw_depth, b->status);
   } else {
     gemv_w4a16_stream_kernel<2><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
-      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->status);
+      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
+      b->plan.x_raw_depth, b->status);
   }
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "gemv_w4a16_stream_kernel launch");
