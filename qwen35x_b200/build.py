@@ -16,6 +16,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "_lib"
 LIB = LIB_DIR / "libq35b.so"
+CLI = LIB_DIR / "q35b"
 
 SOURCES = ["api.cu", "gemv_w4a16.cu", "gemv_stream.cu", "act_quant.cu", "gemm_w4a4_tcgen05.cu", "static_prefill.cu"]
 NVCC_FLAGS = [
@@ -60,7 +61,20 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if force or procs or not LIB.is_file():
         cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static", "-lpthread", "-ldl"]
         subprocess.run(cmd, check=True)
+    build_cli(force=force or bool(procs))
     return LIB
+
+
+def build_cli(force: bool = False) -> Path:
+    """The C++ host mirror of the reference entry points and its command line (qwen35x_b200/_lib/q35b)."""
+    host = CSRC / "host"
+    srcs = [host / "nvfp4_runtime.cpp", host / "q35b_main.cpp"]
+    deps = srcs + [host / "nvfp4_runtime.h", CSRC / "nvfp4_codec.cuh", PKG.parent / "include" / "q35b_nvfp4.h", LIB]
+    if force or _stale(CLI, deps):
+        cmd = [_nvcc(), "-std=c++17", "-O2", "-x", "cu", "-gencode", "arch=compute_100a,code=sm_100a", *map(str, srcs),
+               "-o", str(CLI), f"-L{LIB_DIR}", "-lq35b", "-Xlinker", "-rpath,$ORIGIN", "-cudart", "static"]
+        subprocess.run(cmd, check=True)
+    return CLI
 
 
 if __name__ == "__main__":

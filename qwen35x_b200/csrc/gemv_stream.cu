@@ -50,6 +50,7 @@ constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 
 constexpr int kMaxTilesInSmem = 64;             // tile descriptors staged per CTA
 constexpr int kMaxStages = 8;
 constexpr int kMaxRawDepth = 4;
+constexpr int kZeroHalfs = 256;                 // covers the 8 chunk offsets (32 halfs apart) of a K step
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kXPad = 8;                        // fp16 elements of padding between tokens in shared memory
 
@@ -152,9 +153,10 @@ __device__ __forceinline__ void mma_f16_acc(float (&c)[4], uint32_t a0, uint32_t
     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Unsigned E4M3 byte (bit 7 clear) in bits [27:20] of `placed` -> fp32 (0x7f = 480, subnormals exact).
-__device__ __forceinline__ float ue4m3_placed_to_f32(uint32_t placed) {
-  return __uint_as_float(placed & 0x07f00000u) * 0x1p120f;
+// Unsigned E4M3 byte (bit 7 clear) -> fp32 (0x7f = 480, subnormals exact): the byte placed at bit 20 is the
+// value scaled by 2^-120.  The shift is written as a multiply so that it issues on the FMA pipe.
+__device__ __forceinline__ float ue4m3_to_f32(uint32_t byte) {
+  return __uint_as_float(byte * 0x100000u) * 0x1p120f;
 }
 
 // MT = number of 4-token groups (1 for M <= 4, 2 for M <= 8).
@@ -171,7 +173,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   __half * xbuf = reinterpret_cast<__half *>(ring + stages * kStageBytes);        // 2 buffers of x_buf_halfs
   float * xsbuf = reinterpret_cast<float *>(xbuf + 2 * x_buf_halfs);               // 2 buffers of xs_buf_floats (1/scale)
   float * red = xsbuf + 2 * xs_buf_floats;                                         // 2 x [8 row groups][32 lanes][4*MT]
-  GemvTile * stile = reinterpret_cast<GemvTile *>(red + 2 * kRowGroups * 32 * 4 * MT);
+  __half * zeros = reinterpret_cast<__half *>(red + 2 * kRowGroups * 32 * 4 * MT);    // kZeroHalfs of 0.0
+  GemvTile * stile = reinterpret_cast<GemvTile *>(zeros + kZeroHalfs);
   uint8_t * xraw = reinterpret_cast<uint8_t *>(stile + kMaxTilesInSmem);           // x_raw_depth buffers of x_raw_bytes
   uint64_t * bars = reinterpret_cast<uint64_t *>(xraw + static_cast<size_t>(x_raw_depth) * x_raw_bytes);
   // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2], red_full[2], red_free[2], xraw_full[kMaxRawDepth]
@@ -202,7 +205,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     for (int i = 0; i < x_raw_depth; ++i) mbar_init(smem_u32(xraw_full + i), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // stage this CTA's tile descriptors
+  // stage this CTA's tile descriptors; clear the zero region
+  for (int i = threadIdx.x; i < kZeroHalfs / 2; i += kThreads) reinterpret_cast<uint32_t *>(zeros)[i] = 0u;
   {
     const int n_stage = min(n_tiles, kMaxTilesInSmem);
     constexpr int kWords = sizeof(GemvTile) / 16;
@@ -216,7 +220,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t it = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
       for (int ti = 0; ti < n_tiles && ok; ++ti) {
         const GemvTile * tile = tile_at(ti);
@@ -224,9 +229,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const int k_steps = tile->k_steps;
         const uint8_t * sc = tile->scales;
         const int row0 = tile->row_block * kTileRows;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int stage = it % stages;
-          const uint32_t phase = (it / stages) & 1;
+        for (int ks = 0; ks < k_steps; ++ks) {
           if (!mbar_wait(smem_u32(empty + stage), phase ^ 1)) {
             atomicExch(status, kProducerWait);
             ok = false;
@@ -237,6 +240,10 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           mbar_expect_tx(bar, kStageBytes);
           tma_load_2d(smem_u32(dst), tmap, bar, ks * kStepBytes, row0);
           bulk_load(smem_u32(dst + kCodesBytes), sc + static_cast<size_t>(ks) * kScaleBytes, kScaleBytes, bar);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
       }
     }
@@ -337,7 +344,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     const int sc_off1 = sc_off0 + 8 * 16;  // row r0 + 8 (same 32-row group)
     const int x_lane_off = 16 * hB + 8 * (t & 1);
 
-    uint32_t it = 0;
+    int stage = 0;
+    uint32_t phase = 0;
     uint32_t xi = 0;
     int prev_item = -1;
     int buf = 0;
@@ -369,9 +377,21 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[ts][i] = 0.0f;
 
-      for (int ks = 0; ks < k_steps; ++ks, ++it) {
-        const int stage = it % stages;
-        if (!mbar_wait(smem_u32(full + stage), (it / stages) & 1)) {
+      // B-fragment source of this lane per token group: its slice of the fp16 activations if it owns k-slots of
+      // that MMA column, else a zeroed region (same offsets work in both, so the inner loop has no predicates).
+      const __half * bsrc[MT];
+      int bstep[MT];
+#pragma unroll
+      for (int ts = 0; ts < MT; ++ts) {
+        const int token = 4 * ts + mB;
+        const bool owner = b_owner && token < m_tokens;
+        bsrc[ts] = owner ? xb + static_cast<size_t>(token) * xstride + x_lane_off : zeros;
+        bstep[ts] = owner ? 256 : 0;
+      }
+      const int tok_a = 2 * (t & 1);
+
+      for (int ks = 0; ks < k_steps; ++ks) {
+        if (!mbar_wait(smem_u32(full + stage), phase)) {
           if (lane == 0) atomicExch(status, kConsumerWait);
           ok = false;
           break;
@@ -391,26 +411,21 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           const int pair = 2 * kh + pp;
           uint32_t r[4];
           ldmatrix_x4(codes_addr + (((2 * pair + lm_chunk) ^ lm_xor) << 4), r[0], r[1], r[2], r[3]);
-          // scale words of this pair's 4-block tile: blocks 4*pair .. 4*pair+3 of rows r0 and r0+8
-          const uint32_t w0 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off0);
-          const uint32_t w1 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off1);
+          // scale bytes of this pair's 4-block tile (blocks 4*pair .. 4*pair+3 of rows r0 and r0+8): plain byte
+          // loads keep the integer pipe free for the FP4 conversions
+          const uint8_t * sc0 = sc + pair * 512 + sc_off0 + hD;
 #pragma unroll
           for (int cq = 0; cq < 2; ++cq) {
             const int q = 2 * pair + cq;  // 32-code chunk index inside the K step
             uint32_t a_lo[4], a_hi[4];
             e2m1x8_to_f16(r[2 * cq], a_lo);      // rows 0..7 of the warp's 16
             e2m1x8_to_f16(r[2 * cq + 1], a_hi);  // rows 8..15
-            // block 2*cq + hD of the 4-block tile -> byte (2*cq + hD) of the scale words
-            const int sh = 20 - 8 * (2 * cq + hD);
-            const float s0 = ue4m3_placed_to_f32(sh >= 0 ? (w0 << sh) : (w0 >> (-sh)));
-            const float s1 = ue4m3_placed_to_f32(sh >= 0 ? (w1 << sh) : (w1 >> (-sh)));
+            // block 2*cq + hD of the 4-block tile; rows r0 and r0 + 8 (128 bytes further)
+            const float s0 = ue4m3_to_f32(sc0[2 * cq]);
+            const float s1 = ue4m3_to_f32(sc0[2 * cq + 128]);
 #pragma unroll
             for (int ts = 0; ts < MT; ++ts) {
-              const int token = 4 * ts + mB;
-              uint4 b = make_uint4(0u, 0u, 0u, 0u);
-              if (b_owner && token < m_tokens) {
-                b = *reinterpret_cast<const uint4 *>(xb + static_cast<size_t>(token) * xstride + ks * 256 + 32 * q + x_lane_off);
-              }
+              const uint4 b = *reinterpret_cast<const uint4 *>(bsrc[ts] + 32 * q);
               float c[4];
               mma_f16_zero(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
               mma_f16_acc(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
@@ -423,10 +438,15 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + stage));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
         // undo the activation scale of this K step (tokens 2*(t&1), +1 of each group)
 #pragma unroll
         for (int ts = 0; ts < MT; ++ts) {
-          const int tok0 = 4 * ts + 2 * (t & 1);
+          bsrc[ts] += bstep[ts];
+          const int tok0 = 4 * ts + tok_a;
           const float i0 = (tok0 < m_tokens) ? xs[tok0 * k_steps + ks] : 0.0f;
           const float i1 = (tok0 + 1 < m_tokens) ? xs[(tok0 + 1) * k_steps + ks] : 0.0f;
           acc[ts][0] = fmaf(sacc[ts][0], i0, acc[ts][0]);
@@ -514,7 +534,7 @@ bool make_plan(int m, int max_k, Plan * p) {
   const int mt = m <= 4 ? 1 : 2;
   const int x_halfs = ((m * (max_k + kXPad) + 7) / 8) * 8;
   const int xs_floats = ((m * (max_k / 256) + 3) / 4) * 4;
-  const int fixed = 1024 + 2 * x_halfs * 2 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 +
+  const int fixed = 1024 + 2 * x_halfs * 2 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
                     kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
   const int raw_bytes = ((m * max_k * 2 + 127) / 128) * 128;
   // raw-activation ring: as deep as fits while leaving at least 4 ring stages (3 at the very least)

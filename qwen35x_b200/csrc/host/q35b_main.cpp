@@ -1,0 +1,138 @@
+// q35b command line: the reference CLI's NVFP4 projection modes (src/main.cpp:361-403, 592-758) on the B200 engine.
+//
+//   q35b --check-nvfp4-tensor            [--nvfp4-sample-rows N]
+//   q35b --bench-nvfp4-projection        [--nvfp4-projection-kernel row|warp|scale-group|blackwell-fp4|b200-simt|b200-stream]
+//   q35b --bench-nvfp4-prefill-projection [--nvfp4-prefill-seq-len S]
+//        [--bench-warmup W] [--bench-iters K] --synthetic ROWS,COLS[,SEED]
+//
+// The reference reads the tensor family from --hf-model-dir/--nvfp4-tensor; no checkpoint reader exists here yet, so
+// the tensor comes from --synthetic (fp32 N(0, 0.02) weights quantised with the engine's NVFP4 recipe).
+// Output is the reference's `key: value` block.  Exit codes: 0 ok, 2 usage, 10 failure.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <iostream>
+#include <string>
+#include <vector>
+
+#include "nvfp4_runtime.h"
+
+namespace rt = q35b::runtime;
+
+static void usage() {
+  std::cerr << "usage: q35b (--check-nvfp4-tensor | --bench-nvfp4-projection | --bench-nvfp4-prefill-projection)\n"
+               "            --synthetic ROWS,COLS[,SEED] [--nvfp4-projection-kernel NAME] [--nvfp4-sample-rows N]\n"
+               "            [--nvfp4-prefill-seq-len S] [--bench-warmup W] [--bench-iters K] [--nvfp4-input-scale F]\n";
+}
+
+int main(int argc, char ** argv) {
+  enum Mode { kNone, kCheck, kBench, kPrefill } mode = kNone;
+  std::string kernel = "scale-group";
+  int rows = 0, cols = 0, sample_rows = 16, seq_len = 256, warmup = 5, iters = 20;
+  unsigned long long seed = 42;
+  float input_scale = 1.0f;
+  for (int i = 1; i < argc; ++i) {
+    const std::string a = argv[i];
+    auto value = [&](const char * flag) -> const char * {
+      if (i + 1 >= argc) {
+        std::cerr << flag << " needs a value\n";
+        std::exit(2);
+      }
+      return argv[++i];
+    };
+    if (a == "--check-nvfp4-tensor") mode = kCheck;
+    else if (a == "--bench-nvfp4-projection") mode = kBench;
+    else if (a == "--bench-nvfp4-prefill-projection") mode = kPrefill;
+    else if (a == "--nvfp4-projection-kernel") kernel = value("--nvfp4-projection-kernel");
+    else if (a == "--nvfp4-sample-rows") sample_rows = std::atoi(value("--nvfp4-sample-rows"));
+    else if (a == "--nvfp4-prefill-seq-len") seq_len = std::atoi(value("--nvfp4-prefill-seq-len"));
+    else if (a == "--bench-warmup") warmup = std::atoi(value("--bench-warmup"));
+    else if (a == "--bench-iters") iters = std::atoi(value("--bench-iters"));
+    else if (a == "--nvfp4-input-scale") input_scale = static_cast<float>(std::atof(value("--nvfp4-input-scale")));
+    else if (a == "--synthetic") {
+      const std::string v = value("--synthetic");
+      if (std::sscanf(v.c_str(), "%d,%d,%llu", &rows, &cols, &seed) < 2) {
+        std::cerr << "--synthetic expects ROWS,COLS[,SEED]\n";
+        return 2;
+      }
+    } else if (a == "--help" || a == "-h") {
+      usage();
+      return 0;
+    } else {
+      std::cerr << "unknown argument: " << a << "\n";
+      usage();
+      return 2;
+    }
+  }
+  if (mode == kNone || rows <= 0 || cols <= 0) {
+    usage();
+    return 2;
+  }
+
+  std::string error;
+  std::vector<std::uint8_t> packed, scales;
+  float s2 = 1.0f;
+  if (!rt::make_synthetic_tensor(rows, cols, seed, 0.02f, packed, scales, s2, error)) {
+    std::cerr << "NVFP4 synthetic tensor failed: " << error << "\n";
+    return 10;
+  }
+  const std::string tensor = "synthetic[" + std::to_string(rows) + "," + std::to_string(cols) + "] seed " + std::to_string(seed);
+
+  if (mode == kCheck) {
+    double max_abs_error = 0.0;
+    if (!rt::run_nvfp4_matvec_check(packed, scales, input_scale, s2, rows, cols, sample_rows, max_abs_error, error)) {
+      std::cerr << "NVFP4 tensor check failed: " << error << "\n";
+      return 10;
+    }
+    std::cout << "nvfp4_tensor_check:\n"
+              << "  tensor: " << tensor << "\n"
+              << "  source_shape: [" << rows << ", " << cols << "]\n"
+              << "  packed_shape: [" << rows << ", " << cols / 2 << "]\n"
+              << "  scale_shape: [" << rows << ", " << cols / 16 << "]\n"
+              << "  sample_rows: " << sample_rows << "\n"
+              << "  max_abs_error: " << max_abs_error << "\n";
+    return 0;
+  }
+  if (mode == kBench) {
+    int variant = 0;
+    if (!rt::parse_projection_kernel(kernel, variant, error)) {
+      std::cerr << "NVFP4 projection benchmark failed: " << error << "\n";
+      return 10;
+    }
+    double avg_ms = 0.0, max_abs_error = 0.0;
+    if (!rt::run_nvfp4_custom_projection_benchmark(packed, scales, input_scale, s2, rows, cols, variant, warmup, iters, avg_ms,
+                                                   max_abs_error, error)) {
+      std::cerr << "NVFP4 projection benchmark failed: " << error << "\n";
+      return 10;
+    }
+    const double bytes = static_cast<double>(rows) * cols * (0.5 + 1.0 / 16.0);
+    std::cout << "nvfp4_projection_benchmark:\n"
+              << "  tensor: " << tensor << "\n"
+              << "  kernel: " << kernel << "\n"
+              << "  backend_note: " << rt::projection_kernel_note(variant) << "\n"
+              << "  source_shape: [" << rows << ", " << cols << "]\n"
+              << "  avg_iteration_ms: " << avg_ms << "\n"
+              << "  iterations_per_second: " << 1000.0 / avg_ms << "\n"
+              << "  weight_gbytes_per_second: " << bytes / (avg_ms * 1e-3) / 1e9 << "\n"
+              << "  max_abs_error: " << max_abs_error << "\n";
+    return 0;
+  }
+  // prefill: the reference's input sin((i % 251) * 0.03125) * 0.25 (src/runtime/runtime.cpp:498-501)
+  std::vector<float> input(static_cast<size_t>(seq_len) * cols);
+  for (size_t i = 0; i < input.size(); ++i) input[i] = std::sin(static_cast<float>(i % 251) * 0.03125f) * 0.25f;
+  double avg_ms = 0.0, max_abs_error = 0.0;
+  if (!rt::run_nvfp4_prefill_projection(input.data(), packed, scales, s2, seq_len, rows, cols, warmup, iters, avg_ms,
+                                        max_abs_error, error)) {
+    std::cerr << "NVFP4 prefill projection benchmark failed: " << error << "\n";
+    return 10;
+  }
+  std::cout << "nvfp4_prefill_projection_benchmark:\n"
+            << "  tensor: " << tensor << "\n"
+            << "  source_shape: [" << rows << ", " << cols << "]\n"
+            << "  sequence_length: " << seq_len << "\n"
+            << "  avg_iteration_ms: " << avg_ms << "\n"
+            << "  iterations_per_second: " << 1000.0 / avg_ms << "\n"
+            << "  tflops: " << 2.0 * seq_len * rows * cols / (avg_ms * 1e-3) / 1e12 << "\n"
+            << "  max_abs_error: " << max_abs_error << "\n";
+  return 0;
+}
