@@ -309,21 +309,19 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
         if "not built" in str(e):
             return None
         raise
-    rows_max = max(q.shard_range(n, i, world)[1] for i in range(world))
-    gathered = torch.empty((world, m, rows_max), dtype=torch.bfloat16, device=device) if world > 1 else None
-    pad = torch.zeros((m, rows_max), dtype=torch.bfloat16, device=device) if world > 1 else None
+    from qwen35x_b200 import sharding
+
     flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device=device)
+    full_c = [None]
 
     def one(with_quant: bool, with_gather: bool):
         if with_quant:
             a_codes, a_scales, g = q.quantize_activations(x, scratch=scratch)
         else:
             a_codes, a_scales, g = scratch[0].view(m, k // 2), scratch[1], scratch[2]
+        q.gemm_w4a4(weight, a_codes, a_scales, g, m, out=out)
         if world > 1 and with_gather:
-            q.gemm_w4a4(weight, a_codes, a_scales, g, m, out=pad[:, : weight.rows])
-            dist.all_gather_into_tensor(gathered, pad)
-        else:
-            q.gemm_w4a4(weight, a_codes, a_scales, g, m, out=out)
+            full_c[0] = sharding.all_gather_rows(out, n)
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):

@@ -50,6 +50,9 @@ struct q35b_weight {
   bool has_tmap = false;
   alignas(64) CUtensorMap tmap_codes;  // 2-D map over codes for the GEMM's B tiles
   int tmap_block_n = 0;
+  bool has_tmap2 = false;              // maps of the 2-CTA GEMM: 128-row code boxes and 4-chunk scale boxes
+  alignas(64) CUtensorMap tmap2_codes;
+  alignas(64) CUtensorMap tmap2_sf;
 };
 
 namespace q35b {
@@ -80,5 +83,11 @@ size_t gemv_batch_bytes(const struct q35b_gemv_batch * b);
 int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, int box_rows);
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s);
+
+
+// gemm_w4a4_2cta.cu
+bool gemm_2cta_eligible(const q35b_weight * w, int m);
+int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+                          int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s);
 
 }  // namespace q35b

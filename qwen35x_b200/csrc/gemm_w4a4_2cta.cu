@@ -1,0 +1,413 @@
+// W4A4 prefill GEMM, 2-CTA persistent variant for sm_100a.
+//
+// Same contract as gemm_w4a4_tcgen05.cu (C[M,N] bf16 = (Aq . Wq^T) * g * s2, replacing
+// run_nvfp4_cublaslt_prefill_projection_device, src/runtime/cuda_bench.cu:1056-1167), built for large M:
+//
+//   - a pair of CTAs on neighbouring SMs (cluster of 2) computes one 256 x 256 output tile with
+//     tcgen05.mma.cta_group::2: each CTA stages only its own 128 rows of A and its own 128 rows of B, so the
+//     bytes every SM pulls from L2 per FLOP are 2/3 of the 1-CTA 128 x 256 tile.  No TMA multicast is used:
+//     every load lands in the issuing CTA's own shared memory;
+//   - persistent: 74 pairs walk the tile list (M-tiles fastest, so the pairs in flight share B tiles in L2);
+//     barriers, TMEM and tensor maps are set up once per CTA, not once per tile;
+//   - per K step (256 FP4 columns) a CTA lands A 16 KB + B 16 KB (128B-swizzled TMA boxes) and the scale
+//     factors SFA 2 KB + SFB 4 KB (TMA boxes over the 512-byte scale tiles); 5-stage ring;
+//   - the leader CTA's MMA thread copies scale factors to TMEM in both CTAs (tcgen05.cp.cta_group::2) and
+//     issues four M=256, N=256, K=64 block-scaled MMAs per K step; tcgen05.commit multicasts stage release and
+//     accumulator-ready to both CTAs;
+//   - four epilogue warps per CTA drain that CTA's 128 x 256 fp32 accumulator half from TMEM, scale, convert
+//     and store BF16.
+//
+// Every mbarrier wait is bounded; an expired wait records a code in *status and the role stops, the kernel
+// still runs to its cluster barrier and frees TMEM.
+#include <cuda_bf16.h>
+
+#include "engine.h"
+#include "nvfp4_codec.cuh"
+
+namespace q35b {
+namespace {
+
+constexpr int kCtaRows = 128;            // rows of A and of B staged per CTA
+constexpr int kTile = 256;               // output tile edge of the pair
+constexpr int kStepBytes = 128;          // 256 FP4 columns
+constexpr int kMmaPerStage = 4;
+constexpr int kSfChunk = 512;
+constexpr int kABytes = kCtaRows * kStepBytes;
+constexpr int kBBytes = kCtaRows * kStepBytes;
+constexpr int kSfaBytes = kMmaPerStage * kSfChunk;
+constexpr int kSfbBytes = 2 * kMmaPerStage * kSfChunk;
+constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 38912
+constexpr int kStages = 5;
+constexpr int kThreads = 192;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kAccCols = kTile;
+constexpr int kSfaCols = kMmaPerStage * 4;
+constexpr int kSfbCols = kMmaPerStage * 8;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the pair's leader
+
+enum StatusCode : unsigned { kProducerWait = 21, kMmaWait = 22, kEpilogueWait = 23, kMmaDrainWait = 24 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void * p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Arrive on the barrier at the same offset in CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(bar), "r"(cta));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// TMA box load into this CTA's shared memory, completion bytes go to the pair leader's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap * map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+    "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+      "r"(dst),
+    "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+    : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+    "{\n\t.reg .pred p;\n\t"
+    "elect.sync _|p, 0xffffffff;\n\t"
+    "selp.u32 %0, 1, 0, p;\n\t}"
+    : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ uint64_t desc_k_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+// kind::mxf4nvf4 instruction descriptor: E2M1 x E2M1, K-major, UE4M3 scales, M = 256 (pair), N = 256.
+__device__ __forceinline__ uint32_t instr_desc_pair() {
+  uint32_t d = 0;
+  d |= 1u << 7;
+  d |= 1u << 10;
+  d |= static_cast<uint32_t>(kTile >> 3) << 17;
+  d |= static_cast<uint32_t>(kTile >> 4) << 24;
+  return d;
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tmem_sfa,
+                                          uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+    "{\n\t.reg .pred p;\n\t"
+    "setp.ne.b32 p, %4, 0;\n\t"
+    "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+    "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+    : "memory");
+}
+__device__ __forceinline__ void utccp_sf_pair(uint32_t tmem_dst, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sdesc) : "memory");
+}
+// Arrive (once all earlier tcgen05 work of this thread has retired) on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(static_cast<uint16_t>(3))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+    : "r"(taddr)
+    : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                      const float * __restrict__ g_dev, float s2, int m, int n, int k_bytes, int m_tiles, int num_tiles,
+                      __nv_bfloat16 * __restrict__ c, int ldc, unsigned int * status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t * smem_a = smem;
+  uint8_t * smem_b = smem_a + kStages * kABytes;
+  uint8_t * smem_sfa = smem_b + kStages * kBBytes;
+  uint8_t * smem_sfb = smem_sfa + kStages * kSfaBytes;
+  uint64_t * bars = reinterpret_cast<uint64_t *>(smem_sfb + kStages * kSfbBytes);
+  uint64_t * full = bars;                       // used in the leader: bytes of both CTAs
+  uint64_t * empty = bars + kStages;            // in each CTA: its own stages are free
+  uint64_t * tmem_full = bars + 2 * kStages;    // in each CTA: the accumulator is complete
+  uint64_t * tmem_empty = tmem_full + 1;        // used in the leader: both CTAs have drained their halves
+  uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int sf_col_blocks = k_bytes >> 5;
+  const int k_steps = (sf_col_blocks + kMmaPerStage - 1) / kMmaPerStage;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(smem_u32(full + i), 1);
+      mbar_init(smem_u32(empty + i), 1);
+    }
+    mbar_init(smem_u32(tmem_full), 1);
+    mbar_init(smem_u32(tmem_empty), 8);  // four epilogue warps in each of the two CTAs
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(static_cast<uint32_t>(kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers exist before anything signals across the pair
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_acc = tmem_base;
+  const uint32_t tmem_sfa = tmem_base + kAccCols;
+  const uint32_t tmem_sfb = tmem_sfa + kSfaCols;
+  // An error recorded by an earlier launch: run no tiles (every CTA still goes through alloc, barriers, dealloc).
+  const bool aborted = *reinterpret_cast<volatile unsigned int *>(status) != 0u;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (elect_one() && !aborted) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int tm = tile % m_tiles;
+        const int tn = tile / m_tiles;
+        const int a_row = tm * kTile + static_cast<int>(rank) * kCtaRows;
+        const int b_row = tn * kTile + static_cast<int>(rank) * kCtaRows;
+        const int sfa_chunk0 = (tm * 2 + static_cast<int>(rank)) * sf_col_blocks;
+        const int sfb_chunk0 = (tn * 2) * sf_col_blocks;
+        const int sfb_chunk1 = (tn * 2 + 1) * sf_col_blocks;
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!mbar_wait(smem_u32(empty + stage), phase ^ 1)) {
+            atomicExch(status, kProducerWait);
+            ok = false;
+            break;
+          }
+          const uint32_t leader_full = smem_u32(full + stage) & kPeerMask;
+          if (rank == 0) mbar_expect_tx(smem_u32(full + stage), 2 * kStageBytes);
+          tma_load_2d_pair(smem_u32(smem_a + stage * kABytes), &tmap_a, leader_full, ks * kStepBytes, a_row);
+          tma_load_2d_pair(smem_u32(smem_b + stage * kBBytes), &tmap_b, leader_full, ks * kStepBytes, b_row);
+          tma_load_2d_pair(smem_u32(smem_sfa + stage * kSfaBytes), &tmap_sfa, leader_full, 0, sfa_chunk0 + ks * kMmaPerStage);
+          tma_load_2d_pair(smem_u32(smem_sfb + stage * kSfbBytes), &tmap_sfb, leader_full, 0, sfb_chunk0 + ks * kMmaPerStage);
+          tma_load_2d_pair(smem_u32(smem_sfb + stage * kSfbBytes + kSfaBytes), &tmap_sfb, leader_full, 0,
+                           sfb_chunk1 + ks * kMmaPerStage);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (rank == 0 && elect_one() && !aborted) {
+      const uint32_t idesc = instr_desc_pair();
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t li = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
+        if (!mbar_wait(smem_u32(tmem_empty), (li & 1) ^ 1)) {
+          atomicExch(status, kMmaDrainWait);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!mbar_wait(smem_u32(full + stage), phase)) {
+            atomicExch(status, kMmaWait);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const int valid = min(kMmaPerStage, sf_col_blocks - ks * kMmaPerStage);
+          const uint32_t a_base = smem_u32(smem_a + stage * kABytes);
+          const uint32_t b_base = smem_u32(smem_b + stage * kBBytes);
+          const uint32_t sfa_base = smem_u32(smem_sfa + stage * kSfaBytes);
+          const uint32_t sfb_base = smem_u32(smem_sfb + stage * kSfbBytes);
+          for (int j = 0; j < valid; ++j) {
+            utccp_sf_pair(tmem_sfa + j * 4, desc_sf(sfa_base + j * kSfChunk));
+            utccp_sf_pair(tmem_sfb + j * 8, desc_sf(sfb_base + j * kSfChunk));
+            utccp_sf_pair(tmem_sfb + j * 8 + 4, desc_sf(sfb_base + kSfaBytes + j * kSfChunk));
+          }
+          for (int j = 0; j < valid; ++j) {
+            umma_pair(tmem_acc, desc_k_sw128(a_base + j * 32), desc_k_sw128(b_base + j * 32), idesc, tmem_sfa + j * 4,
+                      tmem_sfb + j * 8, (ks | j) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(smem_u32(empty + stage));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit_pair(smem_u32(tmem_full));
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs): this CTA's 128 rows of the pair's tile ----------------
+    const int quarter = warp & 3;
+    const float alpha = __ldg(g_dev) * s2;
+    uint32_t li = 0;
+    bool ok = !aborted;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
+      const int tm = tile % m_tiles;
+      const int tn = tile / m_tiles;
+      if (!mbar_wait(smem_u32(tmem_full), li & 1)) {
+        if (lane == 0) atomicExch(status, kEpilogueWait);
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = tm * kTile + static_cast<int>(rank) * kCtaRows + quarter * 32 + lane;
+      const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+      __nv_bfloat16 * crow = c + static_cast<size_t>(row) * ldc + static_cast<size_t>(tn) * kTile;
+      const int n_left = n - tn * kTile;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kTile; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 == kTile) {
+          // last TMEM read of this tile: hand the accumulator back before the stores go out
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty), 0);
+        }
+        if (row < m) {
+          if (c0 + 32 <= n_left && ((reinterpret_cast<uintptr_t>(crow + c0) & 15u) == 0)) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t p[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + e * 2]) * alpha,
+                                                               __uint_as_float(r[v * 8 + e * 2 + 1]) * alpha);
+                p[e] = *reinterpret_cast<const uint32_t *>(&h);
+              }
+              *reinterpret_cast<uint4 *>(crow + c0 + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+            }
+          } else {
+            for (int e = 0; e < 32; ++e) {
+              if (c0 + e < n_left) crow[c0 + e] = __float2bfloat16_rn(__uint_as_float(r[e]) * alpha);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();  // neither CTA may leave while its partner can still signal its barriers or read its tiles
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(kTmemCols))
+                 : "memory");
+  }
+}
+
+// 2-D map over a tiled scale array seen as [chunks, 128 x u32]: box = 4 consecutive 512-byte chunks.
+int make_sf_map(CUtensorMap * map, const void * base, long long chunks) {
+  using Fn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                          const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                          CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Fn fn = nullptr;
+  if (fn == nullptr) {
+    void * p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+      return fail(Q35B_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver.");
+    }
+    fn = reinterpret_cast<Fn>(p);
+  }
+  const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(chunks)};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, 4};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(Q35B_ERR_CUDA, "cuTensorMapEncodeTiled(scale factors) failed with CUresult " + std::to_string(static_cast<int>(r)) + ".");
+  }
+  return Q35B_OK;
+}
+
+}  // namespace
+
+bool gemm_2cta_eligible(const q35b_weight * w, int m) {
+  return w->rows >= 256 && m >= 256 && (w->k % 64) == 0;
+}
+
+int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+                          int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s) {
+  static bool attr_set[64] = {false};
+  if (!attr_set[w->device & 63]) {
+    Q35B_CUDA_TRY(cudaFuncSetAttribute(gemm_w4a4_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                  "cudaFuncSetAttribute(2-CTA gemm smem)");
+    attr_set[w->device & 63] = true;
+  }
+  if (!w->has_tmap2) {
+    if (const int st = make_code_map(&w->tmap2_codes, w->codes, w->rows, w->k / 2, kCtaRows)) return st;
+    const long long chunks = static_cast<long long>((w->rows + 127) / 128) * (w->k / 64);
+    if (const int st = make_sf_map(&w->tmap2_sf, w->scales_tiled, chunks)) return st;
+    w->has_tmap2 = true;
+  }
+  CUtensorMap tmap_a, tmap_sfa;
+  if (const int st = make_code_map(&tmap_a, a_codes, m, w->k / 2, kCtaRows)) return st;
+  if (const int st = make_sf_map(&tmap_sfa, a_scales_tiled, static_cast<long long>((m + 127) / 128) * (w->k / 64))) return st;
+  const int m_tiles = (m + kTile - 1) / kTile;
+  const int n_tiles = (w->rows + kTile - 1) / kTile;
+  const int num_tiles = m_tiles * n_tiles;
+  const int pairs = std::max(1, std::min(num_tiles, sm_count() / 2));
+  gemm_w4a4_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, s>>>(tmap_a, w->tmap2_codes, tmap_sfa, w->tmap2_sf, g_dev, w->s2, m,
+                                                               w->rows, w->k / 2, m_tiles, num_tiles,
+                                                               static_cast<__nv_bfloat16 *>(c_bf16), ldc, status_dev);
+  count_launch();
+  Q35B_CUDA_TRY(cudaGetLastError(), "gemm_w4a4_2cta_kernel launch");
+  return Q35B_OK;
+}
+
+}  // namespace q35b

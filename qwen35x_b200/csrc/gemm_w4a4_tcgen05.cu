@@ -442,6 +442,10 @@ int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a
     status_dev = slot;
     Q35B_CUDA_TRY(cudaMemsetAsync(slot, 0, sizeof(unsigned int), s), "cudaMemsetAsync(gemm status)");
   }
+  // Large problems: pairs of CTAs on 256 x 256 tiles, persistent (gemm_w4a4_2cta.cu).
+  if (gemm_2cta_eligible(w, m)) {
+    return launch_gemm_w4a4_2cta(w, a_codes, a_scales_tiled, g_dev, m, c_bf16, ldc, status_dev, s);
+  }
   CUtensorMap tmap_a;
   if (const int st = make_code_map(&tmap_a, a_codes, m, w->k / 2, kBlockM)) return st;
   // Small problems get narrower tiles so that more SMs have work.
