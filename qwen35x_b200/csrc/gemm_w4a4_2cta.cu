@@ -3,18 +3,21 @@
 // Same contract as gemm_w4a4_tcgen05.cu (C[M,N] bf16 = (Aq . Wq^T) * g * s2, replacing
 // run_nvfp4_cublaslt_prefill_projection_device, src/runtime/cuda_bench.cu:1056-1167), built for large M:
 //
-//   - a pair of CTAs on neighbouring SMs (cluster of 2) computes one 256 x 256 output tile with
-//     tcgen05.mma.cta_group::2: each CTA stages only its own 128 rows of A and its own 128 rows of B, so the
-//     bytes every SM pulls from L2 per FLOP are 2/3 of the 1-CTA 128 x 256 tile.  No TMA multicast is used:
-//     every load lands in the issuing CTA's own shared memory;
+//   - a pair of CTAs on neighbouring SMs (cluster of 2) computes one 256 x 192 output tile with
+//     tcgen05.mma.cta_group::2: each CTA stages only its own 128 rows of A and its own 96 rows of B.  No TMA
+//     multicast is used: every load lands in the issuing CTA's own shared memory;
+//   - N = 192 leaves room in TMEM (2 x 192 accumulator columns + 48 scale-factor columns <= 512) for TWO
+//     accumulators, so the epilogue of one tile overlaps the MMAs of the next;
 //   - persistent: 74 pairs walk the tile list (M-tiles fastest, so the pairs in flight share B tiles in L2);
 //     barriers, TMEM and tensor maps are set up once per CTA, not once per tile;
-//   - per K step (256 FP4 columns) a CTA lands A 16 KB + B 16 KB (128B-swizzled TMA boxes) and the scale
-//     factors SFA 2 KB + SFB 4 KB (TMA boxes over the 512-byte scale tiles); 5-stage ring;
+//   - per K step (256 FP4 columns) a CTA lands A 16 KB + B 12 KB (128B-swizzled TMA boxes) and the scale
+//     factors SFA 2 KB + SFB 4 KB (TMA boxes over the 512-byte scale tiles); 6-stage ring.  A 192-row tile
+//     starts either on a 128-row scale tile or 64 rows into one: it always takes two scale tiles, and the MMA's
+//     SFB address is moved by two TMEM columns (= 64 rows) in the second case;
 //   - the leader CTA's MMA thread copies scale factors to TMEM in both CTAs (tcgen05.cp.cta_group::2) and
-//     issues four M=256, N=256, K=64 block-scaled MMAs per K step; tcgen05.commit multicasts stage release and
+//     issues four M=256, N=192, K=64 block-scaled MMAs per K step; tcgen05.commit multicasts stage release and
 //     accumulator-ready to both CTAs;
-//   - four epilogue warps per CTA drain that CTA's 128 x 256 fp32 accumulator half from TMEM, scale, convert
+//   - four epilogue warps per CTA drain that CTA's 128 x 192 fp32 accumulator half from TMEM, scale, convert
 //     and store BF16.
 //
 // Every mbarrier wait is bounded; an expired wait records a code in *status and the role stops, the kernel
@@ -27,20 +30,22 @@
 namespace q35b {
 namespace {
 
-constexpr int kCtaRows = 128;            // rows of A and of B staged per CTA
-constexpr int kTile = 256;               // output tile edge of the pair
+constexpr int kCtaRows = 128;            // rows of A staged per CTA
+constexpr int kTileM = 256;              // output tile of the pair: 256 tokens ...
+constexpr int kTileN = 192;              // ... by 192 weight rows
+constexpr int kCtaBRows = kTileN / 2;    // rows of B staged per CTA
 constexpr int kStepBytes = 128;          // 256 FP4 columns
 constexpr int kMmaPerStage = 4;
 constexpr int kSfChunk = 512;
 constexpr int kABytes = kCtaRows * kStepBytes;
-constexpr int kBBytes = kCtaRows * kStepBytes;
+constexpr int kBBytes = kCtaBRows * kStepBytes;
 constexpr int kSfaBytes = kMmaPerStage * kSfChunk;
 constexpr int kSfbBytes = 2 * kMmaPerStage * kSfChunk;
-constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 38912
-constexpr int kStages = 5;
+constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 34816
+constexpr int kStages = 6;
 constexpr int kThreads = 192;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-constexpr int kAccCols = kTile;
+constexpr int kAccCols = 2 * kTileN;     // two accumulators
 constexpr int kSfaCols = kMmaPerStage * 4;
 constexpr int kSfbCols = kMmaPerStage * 8;
 constexpr int kTmemCols = 512;
@@ -109,13 +114,13 @@ __device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
   d |= static_cast<uint64_t>(1) << 46;
   return d;
 }
-// kind::mxf4nvf4 instruction descriptor: E2M1 x E2M1, K-major, UE4M3 scales, M = 256 (pair), N = 256.
+// kind::mxf4nvf4 instruction descriptor: E2M1 x E2M1, K-major, UE4M3 scales, M = 256 (pair), N = 192.
 __device__ __forceinline__ uint32_t instr_desc_pair() {
   uint32_t d = 0;
   d |= 1u << 7;
   d |= 1u << 10;
-  d |= static_cast<uint32_t>(kTile >> 3) << 17;
-  d |= static_cast<uint32_t>(kTile >> 4) << 24;
+  d |= static_cast<uint32_t>(kTileN >> 3) << 17;
+  d |= static_cast<uint32_t>(kTileM >> 4) << 24;
   return d;
 }
 __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tmem_sfa,
@@ -166,9 +171,9 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint64_t * bars = reinterpret_cast<uint64_t *>(smem_sfb + kStages * kSfbBytes);
   uint64_t * full = bars;                       // used in the leader: bytes of both CTAs
   uint64_t * empty = bars + kStages;            // in each CTA: its own stages are free
-  uint64_t * tmem_full = bars + 2 * kStages;    // in each CTA: the accumulator is complete
-  uint64_t * tmem_empty = tmem_full + 1;        // used in the leader: both CTAs have drained their halves
-  uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 1);
+  uint64_t * tmem_full = bars + 2 * kStages;    // [2] in each CTA: accumulator b is complete
+  uint64_t * tmem_empty = tmem_full + 2;        // [2] used in the leader: both CTAs have drained accumulator b
+  uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -184,8 +189,10 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       mbar_init(smem_u32(full + i), 1);
       mbar_init(smem_u32(empty + i), 1);
     }
-    mbar_init(smem_u32(tmem_full), 1);
-    mbar_init(smem_u32(tmem_empty), 8);  // four epilogue warps in each of the two CTAs
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(tmem_full + i), 1);
+      mbar_init(smem_u32(tmem_empty + i), 8);  // four epilogue warps in each of the two CTAs
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -214,11 +221,12 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int tm = tile % m_tiles;
         const int tn = tile / m_tiles;
-        const int a_row = tm * kTile + static_cast<int>(rank) * kCtaRows;
-        const int b_row = tn * kTile + static_cast<int>(rank) * kCtaRows;
+        const int a_row = tm * kTileM + static_cast<int>(rank) * kCtaRows;
+        const int b_row = tn * kTileN + static_cast<int>(rank) * kCtaBRows;
         const int sfa_chunk0 = (tm * 2 + static_cast<int>(rank)) * sf_col_blocks;
-        const int sfb_chunk0 = (tn * 2) * sf_col_blocks;
-        const int sfb_chunk1 = (tn * 2 + 1) * sf_col_blocks;
+        const int sfb_rb = (tn * kTileN) >> 7;  // first 128-row scale tile the 192 rows touch
+        const int sfb_chunk0 = sfb_rb * sf_col_blocks;
+        const int sfb_chunk1 = (sfb_rb + 1) * sf_col_blocks;
         for (int ks = 0; ks < k_steps; ++ks) {
           if (!mbar_wait(smem_u32(empty + stage), phase ^ 1)) {
             atomicExch(status, kProducerWait);
@@ -249,11 +257,14 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t li = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
-        if (!mbar_wait(smem_u32(tmem_empty), (li & 1) ^ 1)) {
+        const uint32_t ab = li & 1;
+        if (!mbar_wait(smem_u32(tmem_empty + ab), ((li >> 1) & 1) ^ 1)) {
           atomicExch(status, kMmaDrainWait);
           ok = false;
           break;
         }
+        const uint32_t acc = tmem_acc + ab * kTileN;
+        const uint32_t sfb_off = ((static_cast<uint32_t>(tile / m_tiles) * kTileN) & 127u) >> 5;  // 0 or 2 columns
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int ks = 0; ks < k_steps; ++ks) {
           if (!mbar_wait(smem_u32(full + stage), phase)) {
@@ -273,8 +284,8 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             utccp_sf_pair(tmem_sfb + j * 8 + 4, desc_sf(sfb_base + kSfaBytes + j * kSfChunk));
           }
           for (int j = 0; j < valid; ++j) {
-            umma_pair(tmem_acc, desc_k_sw128(a_base + j * 32), desc_k_sw128(b_base + j * 32), idesc, tmem_sfa + j * 4,
-                      tmem_sfb + j * 8, (ks | j) != 0 ? 1u : 0u);
+            umma_pair(acc, desc_k_sw128(a_base + j * 32), desc_k_sw128(b_base + j * 32), idesc, tmem_sfa + j * 4,
+                      tmem_sfb + j * 8 + sfb_off, (ks | j) != 0 ? 1u : 0u);
           }
           umma_commit_pair(smem_u32(empty + stage));
           if (++stage == kStages) {
@@ -282,7 +293,7 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             phase ^= 1;
           }
         }
-        if (ok) umma_commit_pair(smem_u32(tmem_full));
+        if (ok) umma_commit_pair(smem_u32(tmem_full + ab));
       }
     }
   } else {
@@ -294,26 +305,27 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
       const int tm = tile % m_tiles;
       const int tn = tile / m_tiles;
-      if (!mbar_wait(smem_u32(tmem_full), li & 1)) {
+      const uint32_t ab = li & 1;
+      if (!mbar_wait(smem_u32(tmem_full + ab), (li >> 1) & 1)) {
         if (lane == 0) atomicExch(status, kEpilogueWait);
         ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = tm * kTile + static_cast<int>(rank) * kCtaRows + quarter * 32 + lane;
-      const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
-      __nv_bfloat16 * crow = c + static_cast<size_t>(row) * ldc + static_cast<size_t>(tn) * kTile;
-      const int n_left = n - tn * kTile;
+      const int row = tm * kTileM + static_cast<int>(rank) * kCtaRows + quarter * 32 + lane;
+      const uint32_t taddr = tmem_acc + ab * kTileN + (static_cast<uint32_t>(quarter * 32) << 16);
+      __nv_bfloat16 * crow = c + static_cast<size_t>(row) * ldc + static_cast<size_t>(tn) * kTileN;
+      const int n_left = n - tn * kTileN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kTile; c0 += 32) {
+      for (int c0 = 0; c0 < kTileN; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 32 == kTile) {
+        if (c0 + 32 == kTileN) {
           // last TMEM read of this tile: hand the accumulator back before the stores go out
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty), 0);
+          if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + ab), 0);
         }
         if (row < m) {
           if (c0 + 32 <= n_left && ((reinterpret_cast<uintptr_t>(crow + c0) & 15u) == 0)) {
@@ -378,7 +390,7 @@ int make_sf_map(CUtensorMap * map, const void * base, long long chunks) {
 }  // namespace
 
 bool gemm_2cta_eligible(const q35b_weight * w, int m) {
-  return w->rows >= 256 && m >= 256 && (w->k % 64) == 0;
+  return w->rows >= 192 && m >= 256 && (w->k % 64) == 0;
 }
 
 int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
@@ -390,7 +402,7 @@ int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_
     attr_set[w->device & 63] = true;
   }
   if (!w->has_tmap2) {
-    if (const int st = make_code_map(&w->tmap2_codes, w->codes, w->rows, w->k / 2, kCtaRows)) return st;
+    if (const int st = make_code_map(&w->tmap2_codes, w->codes, w->rows, w->k / 2, kCtaBRows)) return st;
     const long long chunks = static_cast<long long>((w->rows + 127) / 128) * (w->k / 64);
     if (const int st = make_sf_map(&w->tmap2_sf, w->scales_tiled, chunks)) return st;
     w->has_tmap2 = true;
@@ -398,8 +410,8 @@ int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_
   CUtensorMap tmap_a, tmap_sfa;
   if (const int st = make_code_map(&tmap_a, a_codes, m, w->k / 2, kCtaRows)) return st;
   if (const int st = make_sf_map(&tmap_sfa, a_scales_tiled, static_cast<long long>((m + 127) / 128) * (w->k / 64))) return st;
-  const int m_tiles = (m + kTile - 1) / kTile;
-  const int n_tiles = (w->rows + kTile - 1) / kTile;
+  const int m_tiles = (m + kTileM - 1) / kTileM;
+  const int n_tiles = (w->rows + kTileN - 1) / kTileN;
   const int num_tiles = m_tiles * n_tiles;
   const int pairs = std::max(1, std::min(num_tiles, sm_count() / 2));
   gemm_w4a4_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, s>>>(tmap_a, w->tmap2_codes, tmap_sfa, w->tmap2_sf, g_dev, w->s2, m,
