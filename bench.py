@@ -388,10 +388,10 @@ def cpu_baseline(sample_layers: int) -> dict:
 
     threads = o.max_threads()
     cpu_decode_sample(o, np, 1, threads)  # warm the pages
-    dt, nbytes = cpu_decode_sample(o, np, sample_layers, threads, repeats=max(1, 24 // sample_layers) * 10)
+    dt, nbytes = cpu_decode_sample(o, np, sample_layers, threads, repeats=max(1, 24 // sample_layers) * 40)
     dt1, nbytes1 = cpu_decode_sample(o, np, 1, 1)
     return {"value": round(nbytes / dt / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"{sample_layers} of 24 layers x {max(1, 24 // sample_layers) * 10} repeats of the decode step (oracle restatement of "
+            "sample": f"{sample_layers} of 24 layers x {max(1, 24 // sample_layers) * 40} repeats of the decode step (oracle restatement of "
                       f"cuda_bench.cu:2091-2100, rows split over OpenMP threads), {dt:.2f} s",
             "single_thread": {"value": round(nbytes1 / dt1 / 1e9, 4), "unit": "GB/s", "cores": 1,
                               "sample": f"1 layer, {dt1:.2f} s"}}
