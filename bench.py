@@ -38,6 +38,9 @@ SHAPES_0P8B = [(4096, 1024), (1024, 2048), (7168, 1024), (1024, 3584)]  # (N, K)
 GEMM_SHAPE = (18432, 2560)  # (N, K): 4B-class gate+up
 GEMM_M = 4096
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes of one launch from the ncu captures summarised under profiles/ (same workloads as below)
+DECODE_DRAM_TRAFFIC_BYTES = 234_155_520 + 5_728_512
+GEMM_DRAM_TRAFFIC_BYTES = 32_959_488 + 98_072_832
 
 
 def algorithmic_bytes(n: int, k: int, m: int) -> int:
@@ -270,7 +273,10 @@ def run_engine(args, rank: int, world: int, local_rank: int) -> dict | None:
                    "l2": f"two weight sets alternated between steps ({2 * step_bytes} B total > {L2_BYTES} B L2)",
                    "parallelism": "replicas only" if world > 1 else "1 GPU"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": DECODE_DRAM_TRAFFIC_BYTES,
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
+                                       "profiles/gemv_w4a16_stream_decode_step_0p8b.md",
+                     "peak_source": pk["source"],
                      "kernel": "gemv_w4a16_stream_kernel (M=1)", "bytes_per_launch": step_bytes // launches_per_step},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 5)},
@@ -353,10 +359,11 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
         "gemm_only": {"ms": round(ms_gemm, 4), "tflops": round(tf, 1)},
         "quant_gemm_gather": {"ms": round(ms_full, 4), "tflops": round(flops / (ms_full * 1e-3) / 1e12, 1)},
         "roofline": {"bound": "tensor", "achieved": round(tf / world, 1), "peak": fp4_peak_nominal, "unit": "TFLOP/s",
-                     "frac": round(tf / world / fp4_peak_nominal, 4), "traffic": None,
+                     "frac": round(tf / world / fp4_peak_nominal, 4),
+                     "traffic": GEMM_DRAM_TRAFFIC_BYTES if world == 1 else None,
                      "peak_source": "nominal dense FP4 (no measured FP4 peak); 4x measured bf16 burst = "
                                     f"{fp4_peak_4x:.0f} TFLOP/s -> frac {tf / world / fp4_peak_4x:.4f}",
-                     "kernel": "gemm_w4a4_tcgen05", "per_gpu": True},
+                     "kernel": "gemm_w4a4_2cta_kernel", "per_gpu": True},
         "l2": "256 MiB buffer zeroed between timed iterations",
     }
 
