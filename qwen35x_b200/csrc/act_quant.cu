@@ -149,46 +149,50 @@ __device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g
   return sb;
 }
 
-// Pass 2: one thread per (row, group of 4 scale columns = 64 elements).
-// Rows [rows, rows_padded) only get zero scale bytes (TILED layout).
+// Pass 2: one thread per 16-element block, so a warp reads 1 KB of contiguous activations and writes 256 bytes of
+// contiguous codes; the four scale bytes of a 64-element group are gathered into lane 0 of each quad with
+// shuffles and stored as one 32-bit word of the tiled layout (or four bytes of the row-major layout).
+// The grid covers roundup(K/16, 4) block slots per row and rows_padded rows: slots past K and rows past `rows`
+// only produce zero scale bytes (TILED layout).
 template <typename T, int RECIPE, bool TILED>
 __global__ void __launch_bounds__(kThreads)
 quantize_nvfp4_kernel(const T * __restrict__ x, int rows, int rows_padded, int k, const float * __restrict__ g_dev,
                       float g_fixed, float * __restrict__ g_out, int swap, uint8_t * __restrict__ codes,
                       uint8_t * __restrict__ scales) {
   const int scale_cols = k >> 4;
-  const int groups = (scale_cols + 3) >> 2;
+  const int slots = ((scale_cols + 3) >> 2) << 2;  // block slots per row, a multiple of 4
   const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<size_t>(rows_padded) * groups) return;
-  const int row = static_cast<int>(idx / groups);
-  const int grp = static_cast<int>(idx % groups);
+  const size_t total = static_cast<size_t>(rows_padded) * slots;
+  // whole quads run or exit together (slots % 4 == 0 and kThreads % 4 == 0), so the shuffles below are safe
+  const bool live = idx < total;
+  const int row = live ? static_cast<int>(idx / slots) : 0;
+  const int b = live ? static_cast<int>(idx % slots) : 0;
   float g = 1.0f;
   if (RECIPE == kEngine) {
     g = (g_dev != nullptr) ? __ldg(g_dev) : g_fixed;
     if (g_out != nullptr && idx == 0) *g_out = g;
   }
-  uint32_t sbytes = 0;
-  if (row < rows) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int b = grp * 4 + j;
-      if (b < scale_cols) {
-        float v[16];
-        load16<T>(x + static_cast<size_t>(row) * k + static_cast<size_t>(b) * 16, v);
-        uint2 packed;
-        const uint32_t sb = quantize_block<RECIPE>(v, g, swap != 0, packed);
-        sbytes |= sb << (8 * j);
-        *reinterpret_cast<uint2 *>(codes + (static_cast<size_t>(row) * k + static_cast<size_t>(b) * 16) / 2) = packed;
-      }
-    }
+  uint32_t sb = 0;
+  if (live && row < rows && b < scale_cols) {
+    float v[16];
+    load16<T>(x + static_cast<size_t>(row) * k + static_cast<size_t>(b) * 16, v);
+    uint2 packed;
+    sb = quantize_block<RECIPE>(v, g, swap != 0, packed);
+    *reinterpret_cast<uint2 *>(codes + (static_cast<size_t>(row) * k + static_cast<size_t>(b) * 16) / 2) = packed;
   }
+  // gather the quad's four scale bytes
+  const int lane = threadIdx.x & 31;
+  uint32_t word = sb;
+  word |= __shfl_sync(0xffffffffu, sb, (lane & ~3) + 1) << 8;
+  word |= __shfl_sync(0xffffffffu, sb, (lane & ~3) + 2) << 16;
+  word |= __shfl_sync(0xffffffffu, sb, (lane & ~3) + 3) << 24;
+  if (!live || (lane & 3) != 0) return;
   if (TILED) {
-    *reinterpret_cast<uint32_t *>(scales + tiled_scale_offset(row, grp * 4, groups * 4)) = sbytes;
+    *reinterpret_cast<uint32_t *>(scales + tiled_scale_offset(row, b, slots)) = word;
   } else if (row < rows) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int b = grp * 4 + j;
-      if (b < scale_cols) scales[static_cast<size_t>(row) * scale_cols + b] = static_cast<uint8_t>(sbytes >> (8 * j));
+      if (b + j < scale_cols) scales[static_cast<size_t>(row) * scale_cols + b + j] = static_cast<uint8_t>(word >> (8 * j));
     }
   }
 }
@@ -249,7 +253,7 @@ int launch_quantize_bf16(const void * x, int m, int k, float global_scale, uint8
     if (const int st = launch_amax(xb, static_cast<size_t>(m) * k, static_cast<unsigned int *>(workspace), g_dev, s)) return st;
   }
   const int rows_padded = round_up_int(m, 128);
-  const size_t threads = static_cast<size_t>(rows_padded) * (((k >> 4) + 3) >> 2);
+  const size_t threads = static_cast<size_t>(rows_padded) * ((((k >> 4) + 3) >> 2) << 2);
   const unsigned blocks = static_cast<unsigned>((threads + kThreads - 1) / kThreads);
   quantize_nvfp4_kernel<__nv_bfloat16, kEngine, true><<<blocks, kThreads, 0, s>>>(
     xb, m, rows_padded, k, dynamic ? g_dev : nullptr, global_scale, dynamic ? nullptr : g_dev, 0, codes, scales_tiled);
@@ -262,7 +266,7 @@ int launch_quantize_reference_recipe(const void * x, int m, int k, int swap, uin
                                      cudaStream_t s) {
   if (const int st = check_quant_args(x, m, k, codes, scales_tiled)) return st;
   const int rows_padded = round_up_int(m, 128);
-  const size_t threads = static_cast<size_t>(rows_padded) * (((k >> 4) + 3) >> 2);
+  const size_t threads = static_cast<size_t>(rows_padded) * ((((k >> 4) + 3) >> 2) << 2);
   const unsigned blocks = static_cast<unsigned>((threads + kThreads - 1) / kThreads);
   quantize_nvfp4_kernel<__nv_bfloat16, kReference, true><<<blocks, kThreads, 0, s>>>(
     static_cast<const __nv_bfloat16 *>(x), m, rows_padded, k, nullptr, 1.0f, nullptr, swap, codes, scales_tiled);
@@ -278,7 +282,7 @@ int launch_quantize_weight_f32(const float * w, int n, int k, uint8_t * codes, u
   }
   if (n <= 0 || k <= 0 || (k % 16) != 0) return fail(Q35B_ERR_SHAPE, "Invalid dimensions for NVFP4 weight quantisation.");
   if (const int st = launch_amax(w, static_cast<size_t>(n) * k, static_cast<unsigned int *>(workspace), s2_dev, s)) return st;
-  const size_t threads = static_cast<size_t>(n) * (((k >> 4) + 3) >> 2);
+  const size_t threads = static_cast<size_t>(n) * ((((k >> 4) + 3) >> 2) << 2);
   const unsigned blocks = static_cast<unsigned>((threads + kThreads - 1) / kThreads);
   quantize_nvfp4_kernel<float, kEngine, false><<<blocks, kThreads, 0, s>>>(w, n, n, k, s2_dev, 1.0f, nullptr, 0, codes,
                                                                           scales_rowmajor);

@@ -274,18 +274,25 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const int valid = min(kMmaPerStage, sf_col_blocks - ks * kMmaPerStage);
-          const uint32_t a_base = smem_u32(smem_a + stage * kABytes);
-          const uint32_t b_base = smem_u32(smem_b + stage * kBBytes);
-          const uint32_t sfa_base = smem_u32(smem_sfa + stage * kSfaBytes);
-          const uint32_t sfb_base = smem_u32(smem_sfb + stage * kSfbBytes);
-          for (int j = 0; j < valid; ++j) {
-            utccp_sf_pair(tmem_sfa + j * 4, desc_sf(sfa_base + j * kSfChunk));
-            utccp_sf_pair(tmem_sfb + j * 8, desc_sf(sfb_base + j * kSfChunk));
-            utccp_sf_pair(tmem_sfb + j * 8 + 4, desc_sf(sfb_base + kSfaBytes + j * kSfChunk));
+          // descriptors of this stage: the address field counts 16-byte units, so stepping a descriptor is an add
+          const uint64_t a_desc = desc_k_sw128(smem_u32(smem_a + stage * kABytes));
+          const uint64_t b_desc = desc_k_sw128(smem_u32(smem_b + stage * kBBytes));
+          const uint64_t sfa_desc = desc_sf(smem_u32(smem_sfa + stage * kSfaBytes));
+          const uint64_t sfb_desc = desc_sf(smem_u32(smem_sfb + stage * kSfbBytes));
+#pragma unroll
+          for (int j = 0; j < kMmaPerStage; ++j) {
+            if (j < valid) {
+              utccp_sf_pair(tmem_sfa + j * 4, sfa_desc + j * (kSfChunk >> 4));
+              utccp_sf_pair(tmem_sfb + j * 8, sfb_desc + j * (kSfChunk >> 4));
+              utccp_sf_pair(tmem_sfb + j * 8 + 4, sfb_desc + (kSfaBytes >> 4) + j * (kSfChunk >> 4));
+            }
           }
-          for (int j = 0; j < valid; ++j) {
-            umma_pair(acc, desc_k_sw128(a_base + j * 32), desc_k_sw128(b_base + j * 32), idesc, tmem_sfa + j * 4,
-                      tmem_sfb + j * 8 + sfb_off, (ks | j) != 0 ? 1u : 0u);
+#pragma unroll
+          for (int j = 0; j < kMmaPerStage; ++j) {
+            if (j < valid) {
+              umma_pair(acc, a_desc + j * 2, b_desc + j * 2, idesc, tmem_sfa + j * 4, tmem_sfb + j * 8 + sfb_off,
+                        (ks | j) != 0 ? 1u : 0u);
+            }
           }
           umma_commit_pair(smem_u32(empty + stage));
           if (++stage == kStages) {
@@ -328,17 +335,20 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + ab), 0);
         }
         if (row < m) {
-          if (c0 + 32 <= n_left && ((reinterpret_cast<uintptr_t>(crow + c0) & 15u) == 0)) {
+          if (c0 + 32 <= n_left && ((reinterpret_cast<uintptr_t>(crow + c0) & 31u) == 0)) {
+            // 32 columns = 64 bytes per row: two 256-bit stores, each a whole 32-byte sector
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t p[4];
+            for (int v = 0; v < 2; ++v) {
+              uint32_t p[8];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + e * 2]) * alpha,
-                                                               __uint_as_float(r[v * 8 + e * 2 + 1]) * alpha);
+              for (int e = 0; e < 8; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 16 + e * 2]) * alpha,
+                                                               __uint_as_float(r[v * 16 + e * 2 + 1]) * alpha);
                 p[e] = *reinterpret_cast<const uint32_t *>(&h);
               }
-              *reinterpret_cast<uint4 *>(crow + c0 + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(crow + c0 + v * 16), "r"(p[0]),
+                           "r"(p[1]), "r"(p[2]), "r"(p[3]), "r"(p[4]), "r"(p[5]), "r"(p[6]), "r"(p[7])
+                           : "memory");
             }
           } else {
             for (int e = 0; e < 32; ++e) {

@@ -18,8 +18,29 @@ def shard_layout(n: int, world: int):
     return out
 
 
+def all_gather_slabs(local, n: int, group=None, out=None):
+    """local: [M, rows_of_this_rank] -> the slabs of all ranks as [world, M, widest] (rank i's slab is
+    result[i, :, :shard_layout(n, world)[i][1]]).  This is the exchange step itself: one collective, and no copy at
+    all when every rank holds the same number of rows."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    layout = shard_layout(n, world)
+    m = local.shape[0]
+    assert local.shape[1] == layout[rank][1]
+    widest = max(c for _, c in layout)
+    padded = local if local.shape[1] == widest else torch.nn.functional.pad(local, (0, widest - local.shape[1]))
+    if out is None:
+        out = torch.empty((world * m, widest), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out.view(torch.uint8), padded.contiguous().view(torch.uint8), group=group)
+    return out.view(world, m, widest)
+
+
 def all_gather_rows(local, n: int, group=None):
-    """local: [M, rows_of_this_rank] on any device -> [M, N] on every rank (NCCL on GPUs, gloo on CPU)."""
+    """local: [M, rows_of_this_rank] on any device -> [M, N] on every rank (NCCL on GPUs, gloo on CPU):
+    all_gather_slabs followed by a copy into row-major [M, N]."""
     import torch
     import torch.distributed as dist
 
