@@ -21,16 +21,16 @@
 // 32-code chunk, token m<4), so one MMA pair yields, in each lane, the dot
 // product of exactly the block that lane loaded: no cross-lane data movement.
 // The E4M3 block scale multiplies that block dot in fp32 and accumulates.
-// Activations are converted BF16 -> fp16 per (token, K step) with an exact
-// power-of-two scale taken from that step's amax, by a dedicated warp that runs
-// one projection ahead (double-buffered), so the conversion is never waited on.
+// Activations are converted BF16 -> fp16 per token with an exact power-of-two
+// scale taken from the token's amax, by a dedicated warp that prefetches the raw
+// activations of the next projections and runs one projection ahead
+// (double-buffered), so the conversion is never waited on.
 //
 // All waits are bounded; on expiry a code is written to the batch's status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <queue>
 #include <vector>
 
 #include "engine.h"
@@ -165,13 +165,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * __restrict__ tiles,
                          const int * __restrict__ cta_begin, int m_tokens, const __nv_bfloat16 * x_override,
                          __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
-                         int x_raw_bytes, int x_raw_depth, unsigned int * status) {
+                         int x_raw_bytes, int x_raw_depth, int x_bufs, unsigned int * status) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled code tiles; pointer arithmetic on the __shared__ array (rather than an
   // integer round trip) keeps every later access a shared-memory access for the compiler.
   uint8_t * ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  __half * xbuf = reinterpret_cast<__half *>(ring + stages * kStageBytes);        // 2 buffers of x_buf_halfs
-  float * xsbuf = reinterpret_cast<float *>(xbuf + 2 * x_buf_halfs);               // 2 buffers of xs_buf_floats (1/scale)
+  __half * xbuf = reinterpret_cast<__half *>(ring + stages * kStageBytes);        // x_bufs (1 or 2) buffers of x_buf_halfs
+  float * xsbuf = reinterpret_cast<float *>(xbuf + x_bufs * x_buf_halfs);          // 2 buffers of xs_buf_floats (1/scale)
   float * red = xsbuf + 2 * xs_buf_floats;                                         // 2 x [8 row groups][32 lanes][4*MT]
   __half * zeros = reinterpret_cast<__half *>(red + 2 * kRowGroups * 32 * 4 * MT);    // kZeroHalfs of 0.0
   GemvTile * stile = reinterpret_cast<GemvTile *>(zeros + kZeroHalfs);
@@ -274,46 +274,52 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         issue_ti = next_run(issue_ti + 1, tl->item);
       }
       const GemvTile * tile = tile_at(proc_ti);
-      const int buf = xi & 1;
+      const int buf = (x_bufs == 2) ? (xi & 1) : 0;
+      const uint32_t xphase = (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1);
       const uint32_t rb = xi % x_raw_depth;
       if (!mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1) ||
-          !mbar_wait(smem_u32(xempty + buf), ((xi >> 1) & 1) ^ 1)) {
+          !mbar_wait(smem_u32(xempty + buf), xphase ^ 1)) {
         if (lane == 0) atomicExch(status, kPrepWait);
         break;
       }
       const int k = tile->k;
-      const int k_steps = tile->k_steps;
       const int xstride = k + kXPad;
       const __nv_bfloat16 * x = reinterpret_cast<const __nv_bfloat16 *>(xraw + static_cast<size_t>(rb) * x_raw_bytes);
       __half * xb = xbuf + buf * x_buf_halfs;
       float * xs = xsbuf + buf * xs_buf_floats;
-      for (int u = 0; u < m_tokens * k_steps; ++u) {
-        const int token = u / k_steps;
-        const int ks = u - token * k_steps;
-        const uint4 q = *reinterpret_cast<const uint4 *>(x + static_cast<size_t>(token) * k + ks * 256 + lane * 8);
-        const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+      for (int token = 0; token < m_tokens; ++token) {
+        const __nv_bfloat16 * xt = x + static_cast<size_t>(token) * k;
+        // exact power-of-two scale putting the token's amax in [2^14, 2^15) (exponent field clamped to stay normal):
+        // fp16 then holds every BF16 significand exactly down to 2^-28 of the amax
         uint32_t amax_bits = 0;
+        for (int i = lane * 8; i < k; i += 256) {
+          const uint4 q = *reinterpret_cast<const uint4 *>(xt + i);
+          const uint32_t r[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          amax_bits = max(amax_bits, (r[j] << 16) & 0x7fffffffu);
-          amax_bits = max(amax_bits, r[j] & 0x7fff0000u);
+          for (int j = 0; j < 4; ++j) {
+            amax_bits = max(amax_bits, (r[j] << 16) & 0x7fffffffu);
+            amax_bits = max(amax_bits, r[j] & 0x7fff0000u);
+          }
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, off));
-        // exact power-of-two scale putting the step's amax in [2^14, 2^15); exponent field clamped to stay normal
         int e = static_cast<int>(amax_bits >> 23);
         e = min(max(e, 16), 254);
         const float scale = __uint_as_float(static_cast<uint32_t>(268 - e) << 23);
         const float inv_scale = __uint_as_float(static_cast<uint32_t>(e - 14) << 23);
-        uint32_t out[4];
+        __half * xo = xb + static_cast<size_t>(token) * xstride;
+        for (int i = lane * 8; i < k; i += 256) {
+          const uint4 q = *reinterpret_cast<const uint4 *>(xt + i);
+          const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+          uint32_t out[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const __half2 h = __floats2half2_rn(__uint_as_float(r[j] << 16) * scale, __uint_as_float(r[j] & 0xffff0000u) * scale);
-          out[j] = *reinterpret_cast<const uint32_t *>(&h);
+          for (int j = 0; j < 4; ++j) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(r[j] << 16) * scale, __uint_as_float(r[j] & 0xffff0000u) * scale);
+            out[j] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+          *reinterpret_cast<uint4 *>(xo + i) = make_uint4(out[0], out[1], out[2], out[3]);
         }
-        *reinterpret_cast<uint4 *>(xb + static_cast<size_t>(token) * xstride + ks * 256 + lane * 8) =
-          make_uint4(out[0], out[1], out[2], out[3]);
-        if (lane == 0) xs[token * k_steps + ks] = inv_scale;
+        if (lane == 0) xs[token] = inv_scale;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(xfull + buf));
@@ -341,7 +347,6 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     // scale word address pieces: row r -> (r % 32) * 16 + (r / 32) * 4 inside a 512-byte tile
     const int r0 = 16 * rg + g;
     const int sc_off0 = (r0 & 31) * 16 + (r0 >> 5) * 4;
-    const int sc_off1 = sc_off0 + 8 * 16;  // row r0 + 8 (same 32-row group)
     const int x_lane_off = 16 * hB + 8 * (t & 1);
 
     int stage = 0;
@@ -358,8 +363,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           if (lane == 0) mbar_arrive(smem_u32(xempty + buf));
         }
         prev_item = tile->item;
-        buf = xi & 1;
-        if (!mbar_wait(smem_u32(xfull + buf), (xi >> 1) & 1)) {
+        buf = (x_bufs == 2) ? (xi & 1) : 0;
+        if (!mbar_wait(smem_u32(xfull + buf), (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1))) {
           if (lane == 0) atomicExch(status, kConsumerXWait);
           ok = false;
           break;
@@ -388,8 +393,6 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         bsrc[ts] = owner ? xb + static_cast<size_t>(token) * xstride + x_lane_off : zeros;
         bstep[ts] = owner ? 256 : 0;
       }
-      const int tok_a = 2 * (t & 1);
-
       for (int ks = 0; ks < k_steps; ++ks) {
         if (!mbar_wait(smem_u32(full + stage), phase)) {
           if (lane == 0) atomicExch(status, kConsumerWait);
@@ -399,12 +402,6 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const uint8_t * codes = ring + stage * kStageBytes;
         const uint8_t * sc = codes + kCodesBytes;
         const uint32_t codes_addr = smem_u32(codes) + lm_row_off;
-
-        float sacc[MT][4];
-#pragma unroll
-        for (int ts = 0; ts < MT; ++ts)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) sacc[ts][i] = 0.0f;
 
 #pragma unroll
         for (int pp = 0; pp < 2; ++pp) {
@@ -429,10 +426,10 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
               float c[4];
               mma_f16_zero(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
               mma_f16_acc(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
-              sacc[ts][0] = fmaf(c[0], s0, sacc[ts][0]);
-              sacc[ts][1] = fmaf(c[1], s0, sacc[ts][1]);
-              sacc[ts][2] = fmaf(c[2], s1, sacc[ts][2]);
-              sacc[ts][3] = fmaf(c[3], s1, sacc[ts][3]);
+              acc[ts][0] = fmaf(c[0], s0, acc[ts][0]);
+              acc[ts][1] = fmaf(c[1], s0, acc[ts][1]);
+              acc[ts][2] = fmaf(c[2], s1, acc[ts][2]);
+              acc[ts][3] = fmaf(c[3], s1, acc[ts][3]);
             }
           }
         }
@@ -442,18 +439,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           stage = 0;
           phase ^= 1;
         }
-        // undo the activation scale of this K step (tokens 2*(t&1), +1 of each group)
 #pragma unroll
-        for (int ts = 0; ts < MT; ++ts) {
-          bsrc[ts] += bstep[ts];
-          const int tok0 = 4 * ts + tok_a;
-          const float i0 = (tok0 < m_tokens) ? xs[tok0 * k_steps + ks] : 0.0f;
-          const float i1 = (tok0 + 1 < m_tokens) ? xs[(tok0 + 1) * k_steps + ks] : 0.0f;
-          acc[ts][0] = fmaf(sacc[ts][0], i0, acc[ts][0]);
-          acc[ts][1] = fmaf(sacc[ts][1], i1, acc[ts][1]);
-          acc[ts][2] = fmaf(sacc[ts][2], i0, acc[ts][2]);
-          acc[ts][3] = fmaf(sacc[ts][3], i1, acc[ts][3]);
-        }
+        for (int ts = 0; ts < MT; ++ts) bsrc[ts] += bstep[ts];
       }
       if (!ok) break;
 
@@ -502,8 +489,9 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               if (tok0 + e < m_tokens) {
-                if (row_a < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a] = __float2bfloat16_rn(acc[ts][e] * s2);
-                if (row_a + 8 < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a + 8] = __float2bfloat16_rn(acc[ts][2 + e] * s2);
+                const float unscale = xs[tok0 + e] * s2;  // undo the token's fp16 scaling, apply weight_scale_2
+                if (row_a < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a] = __float2bfloat16_rn(acc[ts][e] * unscale);
+                if (row_a + 8 < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a + 8] = __float2bfloat16_rn(acc[ts][2 + e] * unscale);
               }
             }
           }
@@ -526,6 +514,7 @@ struct Plan {
   int xs_buf_floats = 0;
   int x_raw_bytes = 0;
   int x_raw_depth = 0;
+  int x_bufs = 0;
   int smem_bytes = 0;
 };
 
@@ -533,22 +522,29 @@ struct Plan {
 bool make_plan(int m, int max_k, Plan * p) {
   const int mt = m <= 4 ? 1 : 2;
   const int x_halfs = ((m * (max_k + kXPad) + 7) / 8) * 8;
-  const int xs_floats = ((m * (max_k / 256) + 3) / 4) * 4;
-  const int fixed = 1024 + 2 * x_halfs * 2 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
-                    kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
+  const int xs_floats = 8;
   const int raw_bytes = ((m * max_k * 2 + 127) / 128) * 128;
-  // raw-activation ring: as deep as fits while leaving at least 4 ring stages (3 at the very least)
-  int depth = kMaxRawDepth;
-  while (depth > 1 && (kSmemBudget - fixed - depth * raw_bytes) / kStageBytes < 4) --depth;
-  const int stages = std::min(kMaxStages, (kSmemBudget - fixed - depth * raw_bytes) / kStageBytes);
-  if (stages < 3) return false;
-  p->stages = stages;
-  p->x_buf_halfs = x_halfs;
-  p->xs_buf_floats = xs_floats;
-  p->x_raw_bytes = raw_bytes;
-  p->x_raw_depth = depth;
-  p->smem_bytes = fixed + depth * raw_bytes + stages * kStageBytes;
-  return true;
+  const int base = 1024 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
+                   kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
+  // Prefer two fp16 activation buffers and a deep raw-activation ring; give those up (one buffer, shallower ring)
+  // before giving up ring stages below 4.
+  for (int bufs = 2; bufs >= 1; --bufs) {
+    for (int depth = (bufs == 2 ? kMaxRawDepth : 2); depth >= 1; --depth) {
+      const int fixed = base + bufs * x_halfs * 2 + depth * raw_bytes;
+      const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
+      if (stages >= 4 || (bufs == 1 && depth == 1 && stages >= 3)) {
+        p->stages = stages;
+        p->x_buf_halfs = x_halfs;
+        p->xs_buf_floats = xs_floats;
+        p->x_raw_bytes = raw_bytes;
+        p->x_raw_depth = depth;
+        p->x_bufs = bufs;
+        p->smem_bytes = fixed + stages * kStageBytes;
+        return true;
+      }
+    }
+  }
+  return false;
 }
 
 }  // namespace
@@ -606,7 +602,6 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
   }
   const int grid_max = sm_count();
 
-  // Tiles, heaviest first, dealt to the least loaded CTA; each CTA then walks its tiles grouped by projection.
   std::vector<GemvTile> all;
   std::vector<GemvItem> h_items(count);
   for (int i = 0; i < count; ++i) {
@@ -640,16 +635,22 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
     b->bytes_per_run += w->codes_bytes + w->scales_bytes;
   }
   const int grid = std::max(1, std::min<int>(grid_max, static_cast<int>(all.size())));
-  std::stable_sort(all.begin(), all.end(), [](const GemvTile & a, const GemvTile & c) { return a.k_steps > c.k_steps; });
-  using Load = std::pair<long, int>;
-  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
-  for (int c = 0; c < grid; ++c) heap.push({0, c});
   std::vector<std::vector<GemvTile>> per_cta(grid);
-  for (const GemvTile & tl : all) {
-    Load l = heap.top();
-    heap.pop();
-    per_cta[l.second].push_back(tl);
-    heap.push({l.first + tl.k_steps + 1, l.second});
+  {
+    // Each CTA gets a contiguous run of tiles (projection-major order) of about equal cost: it changes projection,
+    // and therefore converts a new activation vector, as rarely as possible, and neighbouring CTAs stream
+    // neighbouring rows.  A tile goes to the CTA in whose share of the total cost its midpoint falls, so no CTA
+    // exceeds its share by more than half a tile.
+    long total = 0;
+    for (const GemvTile & tl : all) total += tl.k_steps + 1;
+    long done = 0;
+    int c = 0;
+    for (const GemvTile & tl : all) {
+      const long cost = tl.k_steps + 1;
+      while (c + 1 < grid && (done + cost / 2) * grid >= static_cast<long>(c + 1) * total) ++c;
+      per_cta[c].push_back(tl);
+      done += cost;
+    }
   }
   std::vector<GemvTile> h_tiles;
   std::vector<int> h_begin(grid + 1, 0);
@@ -703,11 +704,11 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   if (b->m <= 4) {
     gemv_w4a16_stream_kernel<1><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
       b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
-      b->plan.x_raw_depth, b->status);
+      b->plan.x_raw_depth, b->plan.x_bufs, b->status);
   } else {
     gemv_w4a16_stream_kernel<2><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
       b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
-      b->plan.x_raw_depth, b->status);
+      b->plan.x_raw_depth, b->plan.x_bufs, b->status);
   }
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "gemv_w4a16_stream_kernel launch");
