@@ -432,6 +432,38 @@ def cpu_baseline(sample_layers: int) -> dict:
                               "sample": f"1 layer, {dt1:.2f} s"}}
 
 
+def cpu_reference_entries(shapes_m):
+    """CPU leg of the shape report: the oracle's scalar loop (reference CPU path) on a bounded sample of each shape
+    (64 output rows per thread x min(M, 2) tokens), one thread and all threads; the full-shape time is an explicit
+    extrapolation."""
+    import time
+
+    import numpy as np
+
+    from oracle import q35oracle as o
+
+    out = []
+    rng = np.random.default_rng(5)
+    threads = o.max_threads()
+    for n, k, m in shapes_m:
+        rows, toks = min(n, 64 * threads), min(m, 2)
+        codes = rng.integers(0, 256, size=(rows, k // 2), dtype=np.uint8)
+        scales = rng.integers(0x20, 0x50, size=(rows, k // 16), dtype=np.uint8)
+        xb = o.bf16_round(rng.standard_normal((toks, k)).astype(np.float32))
+        res = {}
+        for t in (1, threads):
+            r = min(rows, 64) if t == 1 else rows
+            t0 = time.perf_counter()
+            o.gemv_bf16(codes[:r], scales[:r], 3e-4, xb, threads=t)
+            dt = time.perf_counter() - t0
+            res[t] = dt * (n / r) * (m / toks)
+        out.append({"N": n, "K": k, "M": m, "cpu_us_1_thread_extrapolated": round(res[1] * 1e6, 1),
+                    f"cpu_us_{threads}_threads_extrapolated": round(res[threads] * 1e6, 1), "cores": threads,
+                    "sample": f"{rows} rows x {toks} tokens measured, scaled by rows and tokens"})
+    return out
+
+
+
 def run_reference(args, rank: int) -> dict | None:
     if rank != 0:
         return None
@@ -470,6 +502,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["engine", "reference"], default="engine")
+    ap.add_argument("--report", default="", help="write the per-shape throughput report (JSON) to this path and exit")
     ap.add_argument("--only", choices=["all", "decode", "gemm"], default="all",
                     help="profiling aid: 'decode' skips the GEMM, the per-projection-launch figure and the CPU "
                          "baseline; 'gemm' shrinks the decode part to its minimum")
@@ -478,6 +511,19 @@ def main() -> int:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.report:
+        import torch
+
+        import qwen35x_b200 as q
+        from qwen35x_b200 import shape_report
+
+        torch.cuda.set_device(0)
+        rep = shape_report.run("", q, torch, torch.device("cuda", 0), peaks())
+        rep["cpu_reference"] = cpu_reference_entries([(3584, 1024, 1), (18432, 2560, 1), (2560, 9216, 1), (18432, 2560, 4096)])
+        Path(args.report).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.report).write_text(json.dumps(rep, indent=1))
+        print(json.dumps({"report": args.report, "entries": sum(len(v) for v in rep.values() if isinstance(v, list))}))
+        return 0
     if args.impl == "reference":
         out = run_reference(args, rank)
         if out is not None:

@@ -260,8 +260,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     int proc_ti = issue_ti;
     uint32_t xi = 0;
     while (proc_ti < n_tiles) {
-      // keep up to x_raw_depth raw copies in flight
-      while (issue_ti < n_tiles && issued < xi + static_cast<uint32_t>(x_raw_depth)) {
+      // keep up to x_raw_depth raw copies in flight (none when the plan has no room for a raw ring)
+      while (x_raw_depth > 0 && issue_ti < n_tiles && issued < xi + static_cast<uint32_t>(x_raw_depth)) {
         const GemvTile * tl = tile_at(issue_ti);
         if (lane == 0) {
           const uint32_t rb = issued % x_raw_depth;
@@ -276,15 +276,17 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       const GemvTile * tile = tile_at(proc_ti);
       const int buf = (x_bufs == 2) ? (xi & 1) : 0;
       const uint32_t xphase = (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1);
-      const uint32_t rb = xi % x_raw_depth;
-      if (!mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1) ||
+      const uint32_t rb = x_raw_depth > 0 ? xi % x_raw_depth : 0;
+      if ((x_raw_depth > 0 && !mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1)) ||
           !mbar_wait(smem_u32(xempty + buf), xphase ^ 1)) {
         if (lane == 0) atomicExch(status, kPrepWait);
         break;
       }
       const int k = tile->k;
       const int xstride = k + kXPad;
-      const __nv_bfloat16 * x = reinterpret_cast<const __nv_bfloat16 *>(xraw + static_cast<size_t>(rb) * x_raw_bytes);
+      const __nv_bfloat16 * x = x_raw_depth > 0
+                                  ? reinterpret_cast<const __nv_bfloat16 *>(xraw + static_cast<size_t>(rb) * x_raw_bytes)
+                                  : (x_override != nullptr ? x_override : tile->x);
       __half * xb = xbuf + buf * x_buf_halfs;
       float * xs = xsbuf + buf * xs_buf_floats;
       for (int token = 0; token < m_tokens; ++token) {
@@ -529,10 +531,10 @@ bool make_plan(int m, int max_k, Plan * p) {
   // Prefer two fp16 activation buffers and a deep raw-activation ring; give those up (one buffer, shallower ring)
   // before giving up ring stages below 4.
   for (int bufs = 2; bufs >= 1; --bufs) {
-    for (int depth = (bufs == 2 ? kMaxRawDepth : 2); depth >= 1; --depth) {
+    for (int depth = (bufs == 2 ? kMaxRawDepth : 2); depth >= (bufs == 2 ? 1 : 0); --depth) {
       const int fixed = base + bufs * x_halfs * 2 + depth * raw_bytes;
       const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
-      if (stages >= 4 || (bufs == 1 && depth == 1 && stages >= 3)) {
+      if (stages >= 4 || (bufs == 1 && depth == 0 && stages >= 3)) {
         p->stages = stages;
         p->x_buf_halfs = x_halfs;
         p->xs_buf_floats = xs_floats;

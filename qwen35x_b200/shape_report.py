@@ -1,0 +1,201 @@
+"""Per-shape throughput report of the NVFP4 projection path on one GPU.
+
+Covers the named shapes of the benchmark configurations: the single 0.8B gate_proj projection, the 0.8B and 4B-class
+decode steps at M = 1, 2, 4, 8 (work-list launch), the 4B-class prefill GEMMs at M = 512 and 4096 (GEMM alone and
+activation quantisation + GEMM), and the (K, N) x M sweep with 1 % of weight rows scaled x8.  Every entry gives
+microseconds, GB/s of algorithmic bytes (decode) or TFLOP/s (prefill), and the fraction of the HBM or FP4-tensor
+roofline.  Inputs are seeded synthetic tensors quantised on the GPU; weights are rotated through enough copies that
+no launch finds its operands in L2.
+
+    python bench.py --report gpurun_out/shape_report.json
+"""
+from __future__ import annotations
+
+import json
+import statistics
+
+L2_BYTES = 126 * 1024 * 1024
+FP4_NOMINAL_TFLOPS = 9000.0
+
+
+def _alg_bytes(n, k, m):
+    return n * k // 2 + n * k // 16 + m * k * 2 + m * n * 2 + 4
+
+
+def _copies_for(nbytes: int, limit: int = 96) -> int:
+    return max(2, min(limit, -(-int(1.5 * L2_BYTES) // max(nbytes, 1))))
+
+
+def _make_weight(q, torch, device, gen, n, k, row_outliers=False):
+    w = torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * 0.02
+    if row_outliers:
+        idx = torch.randperm(n, generator=gen, device=device)[: max(1, -(-n // 100))]
+        w[idx] *= 8.0
+    codes, scales, s2 = q.quantize_weight(w)
+    return codes, scales, s2
+
+
+def _time_graphs(torch, stream, graphs, reps: int) -> float:
+    """Median microseconds per replay, cycling through `graphs`, CUDA events on the launching stream."""
+    with torch.cuda.stream(stream):
+        for i in range(max(3, len(graphs))):
+            graphs[i % len(graphs)].replay()
+        stream.synchronize()
+        times = []
+        for block in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(reps):
+                graphs[(block * reps + i) % len(graphs)].replay()
+            e1.record(stream)
+            stream.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / reps)
+    return statistics.median(times)
+
+
+def _capture(torch, stream, fn):
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+    return g
+
+
+def decode_entries(q, torch, device, peaks, shapes, layers, ms, label, row_outliers=False):
+    """Work-list launch over `layers` x `shapes` projections for every M in `ms`."""
+    out = []
+    gen = torch.Generator(device=device).manual_seed(4242)
+    step_weight_bytes = layers * sum(n * k // 2 + n * k // 16 for n, k in shapes)
+    sets = 2 if step_weight_bytes < 2 * L2_BYTES else 1
+    weights = []
+    for _ in range(sets):
+        ws = []
+        for _layer in range(layers):
+            for n, k in shapes:
+                codes, scales, s2 = _make_weight(q, torch, device, gen, n, k, row_outliers)
+                ws.append(q.Nvfp4Weight.from_device(codes, scales, s2))
+                del codes, scales
+        weights.append(ws)
+    stream = torch.cuda.Stream(device=device)
+    for m in ms:
+        xs = [torch.randn((m, k), generator=gen, device=device).to(torch.bfloat16) for _ in range(layers) for _, k in shapes]
+        ys = [torch.empty((m, n), dtype=torch.bfloat16, device=device) for _ in range(layers) for n, _ in shapes]
+        kernel = "gemv_w4a16_stream_kernel (work list)"
+        try:
+            batches = [q.GemvBatch(list(zip(ws, xs, ys)), m) for ws in weights]
+            graphs = [_capture(torch, stream, b.run) for b in batches]
+        except q.Q35bError as e:
+            # activations too large for the streaming kernel's shared memory: per-projection SIMT launches
+            kernel = f"gemv_w4a16_simt_kernel per projection ({e})"
+            batches = []
+
+            def run_set(ws):
+                for w, x, y in zip(ws, xs, ys):
+                    q.gemv_w4a16(w, x, out=y, kernel=q.GEMV_SIMT)
+
+            graphs = [_capture(torch, stream, lambda ws=ws: run_set(ws)) for ws in weights]
+        us = _time_graphs(torch, stream, graphs, reps=10)
+        nbytes = layers * sum(_alg_bytes(n, k, m) for n, k in shapes)
+        gbs = nbytes / us / 1e3
+        for b in batches:
+            if b.status() != 0:
+                raise RuntimeError(f"device-side wait expired, code {b.status()}")
+        out.append({"workload": label, "M": m, "projections": layers * len(shapes), "bytes": nbytes, "us": round(us, 2),
+                    "GB/s": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 4), "kernel": kernel})
+        del batches, graphs
+    return out
+
+
+def single_projection_entries(q, torch, device, peaks, n, k, ms, label, row_outliers=False):
+    """One projection per launch: SIMT and streaming kernels, weights rotated through > L2 worth of copies."""
+    out = []
+    gen = torch.Generator(device=device).manual_seed(99)
+    wbytes = n * k // 2 + n * k // 16
+    copies = _copies_for(wbytes)
+    codes, scales, s2 = _make_weight(q, torch, device, gen, n, k, row_outliers)
+    weights = [q.Nvfp4Weight.from_device(codes, scales, s2) for _ in range(copies)]
+    stream = torch.cuda.Stream(device=device)
+    for m in ms:
+        x = torch.randn((m, k), generator=gen, device=device).to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+        for kernel, name in ((q.GEMV_SIMT, "gemv_w4a16_simt_kernel"), (q.GEMV_STREAM, "gemv_w4a16_stream_kernel")):
+            try:
+                graphs = [_capture(torch, stream, lambda w=w: q.gemv_w4a16(w, x, out=y, kernel=kernel)) for w in weights]
+            except q.Q35bError:
+                continue
+            us = _time_graphs(torch, stream, graphs, reps=copies)
+            nbytes = _alg_bytes(n, k, m)
+            gbs = nbytes / us / 1e3
+            out.append({"workload": label, "M": m, "N": n, "K": k, "bytes": nbytes, "us": round(us, 2),
+                        "GB/s": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 4), "kernel": name,
+                        "l2": f"{copies} weight copies rotated"})
+    return out
+
+
+def gemm_entries(q, torch, device, peaks, n, k, ms, label, row_outliers=False):
+    out = []
+    gen = torch.Generator(device=device).manual_seed(7 + n + k)
+    stream = torch.cuda.Stream(device=device)
+    for m in ms:
+        per_set = n * k * 9 // 16 + m * k * 9 // 16 + m * n * 2
+        sets = max(2, min(6, -(-int(1.3 * L2_BYTES) // per_set)))
+        data = []
+        for _ in range(sets):
+            codes, scales, s2 = _make_weight(q, torch, device, gen, n, k, row_outliers)
+            w = q.Nvfp4Weight.from_device(codes, scales, s2)
+            del codes, scales
+            x = torch.randn((m, k), generator=gen, device=device)
+            x[:, torch.randperm(k, generator=gen, device=device)[: max(1, -(-k // 1000))]] *= 20.0
+            x = x.to(torch.bfloat16)
+            scratch = q.act_scratch(m, k, device)
+            y = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+            q.project_prefill(w, x, out=y, scratch=scratch)
+            data.append((w, x, scratch, y))
+        torch.cuda.synchronize()
+
+        def gemm_only(d):
+            w, x, scratch, y = d
+            q.gemm_w4a4(w, scratch[0].view(m, k // 2), scratch[1], scratch[2], m, out=y)
+
+        def quant_gemm(d):
+            w, x, scratch, y = d
+            q.project_prefill(w, x, out=y, scratch=scratch)
+
+        flops = 2.0 * m * n * k
+        row = {"workload": label, "M": m, "N": n, "K": k, "GFLOP": round(flops / 1e9, 1), "l2": f"{sets} operand sets rotated"}
+        for name, fn in (("gemm_only", gemm_only), ("quant_gemm", quant_gemm)):
+            graphs = [_capture(torch, stream, lambda d=d: fn(d)) for d in data]
+            us = _time_graphs(torch, stream, graphs, reps=sets * 2)
+            tf = flops / us / 1e6
+            row[name] = {"us": round(us, 2), "TFLOP/s": round(tf, 1), "fp4_nominal_frac": round(tf / FP4_NOMINAL_TFLOPS, 4),
+                         "frac_of_4x_measured_bf16": round(tf / (4 * peaks["bf16_tflops"]), 4)}
+        row["kernel"] = "gemm_w4a4_2cta_kernel" if (m >= 256 and n >= 192) else "gemm_w4a4_tcgen05_kernel"
+        out.append(row)
+        del data
+        torch.cuda.empty_cache()
+    return out
+
+
+def run(path: str, q, torch, device, peaks) -> dict:
+    shapes_0p8b = [(4096, 1024), (1024, 2048), (7168, 1024), (1024, 3584)]
+    shapes_4b = [(18432, 2560), (2560, 9216), (10240, 2560), (2560, 4096)]
+    sweep = [(3584, 1024), (9216, 2560), (2560, 9216), (32768, 2560)]  # (N, K)
+    report = {"peaks": peaks, "decode": [], "single_projection": [], "prefill": [], "sweep_decode": [], "sweep_prefill": []}
+    report["single_projection"] += single_projection_entries(q, torch, device, peaks, 3584, 1024, [1],
+                                                             "config 1: 0.8B gate_proj, single projection")
+    report["decode"] += decode_entries(q, torch, device, peaks, shapes_0p8b, 24, [1, 2, 4, 8], "config 2: 0.8B-class decode step")
+    report["decode"] += decode_entries(q, torch, device, peaks, shapes_4b, 32, [1, 2, 4, 8], "config 3: 4B-class decode step")
+    torch.cuda.empty_cache()
+    for n, k in ((18432, 2560), (2560, 9216)):
+        report["prefill"] += gemm_entries(q, torch, device, peaks, n, k, [512, 4096], "config 4: 4B-class prefill")
+    for n, k in sweep:
+        report["sweep_decode"] += single_projection_entries(q, torch, device, peaks, n, k, [1], "config 5 sweep (1% rows x8)",
+                                                            row_outliers=True)
+        report["sweep_prefill"] += gemm_entries(q, torch, device, peaks, n, k, [16, 128, 1024, 4096],
+                                                "config 5 sweep (1% rows x8)", row_outliers=True)
+    if path:
+        with open(path, "w") as f:
+            json.dump(report, f, indent=1)
+    return report
