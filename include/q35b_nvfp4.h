@@ -89,6 +89,23 @@ Q35B_API int q35b_weight_create_from_device(const uint8_t * codes_dev, const uin
                                             float weight_scale_2, float input_scale, int n, int k, int shard_index,
                                             int shard_count, q35b_stream stream, q35b_weight ** out);
 
+/* A gate_proj / up_proj pair as ONE weight whose rows alternate in groups of eight (8 gate rows, 8 up rows, ...),
+ * so that a work-list projection over it can finish with y[j] = bf16(silu(gate_j . x) * (up_j . x)), j < n_half: the
+ * fused epilogue of matvec_gate_up_silu_nvfp4 (src/kernels/cuda/decode_layers.cuh:339-365) and of the
+ * silu_multiply_kernel bridges (src/runtime/cuda_bench.cu:215-222), silu(g) = g / (1 + exp(-g)).  Each half keeps its
+ * own weight_scale_2.  n_half must be a multiple of 8.  Host tensors in checkpoint layout. */
+Q35B_API int q35b_weight_create_gate_up(const uint8_t * gate_codes_host, const uint8_t * gate_scales_host,
+                                        float gate_weight_scale_2, const uint8_t * up_codes_host,
+                                        const uint8_t * up_scales_host, float up_weight_scale_2, int n_half, int k,
+                                        q35b_weight ** out);
+/* 1 if the weight was built by q35b_weight_create_gate_up. */
+Q35B_API int q35b_weight_is_gate_up(const q35b_weight * w);
+
+/* NVFP4 -> BF16 dequantisation of the whole weight, w_bf16 [rows, K] device: bf16(e2m1 * (e4m3 * s2)), the
+ * conversion the reference does on the CPU at load for its BF16 prefill path
+ * (src/runtime/qwen35x_cuda_backend.cpp:742-755). */
+Q35B_API int q35b_weight_dequant_bf16(const q35b_weight * w, void * w_bf16, q35b_stream stream);
+
 Q35B_API void q35b_weight_destroy(q35b_weight * w);
 
 /* Shard geometry: first global row and row count held by this weight. */
@@ -123,8 +140,11 @@ Q35B_API int q35b_gemv_w4a16_f32(const q35b_weight * w, const float * x_f32, flo
  * The items are independent: no projection may read another one's output in the same run. */
 typedef struct q35b_gemv_item {
   const q35b_weight * weight;
-  const void * x_bf16; /* [m, K] device */
-  void * y_bf16;       /* [m, rows] device */
+  const void * x_bf16;        /* [m, K] device */
+  void * y_bf16;              /* [m, out_rows] device; out_rows = rows, or rows/2 for a gate/up weight */
+  const void * residual_bf16; /* NULL, or [m, rows] device: y = bf16(projection + residual), the fused epilogue of
+                                 matvec_down_residual_nvfp4 / matvec_o_residual_nvfp4
+                                 (src/kernels/cuda/decode_layers.cuh:404-428, 465-489) */
 } q35b_gemv_item;
 
 typedef struct q35b_gemv_batch q35b_gemv_batch;

@@ -199,6 +199,39 @@ int q35b_weight_create_from_device(const uint8_t * codes_dev, const uint8_t * sc
   return Q35B_OK;
 }
 
+int q35b_weight_create_gate_up(const uint8_t * gate_codes_host, const uint8_t * gate_scales_host, float gate_weight_scale_2,
+                               const uint8_t * up_codes_host, const uint8_t * up_scales_host, float up_weight_scale_2,
+                               int n_half, int k, q35b_weight ** out) {
+  if (gate_codes_host == nullptr || gate_scales_host == nullptr || up_codes_host == nullptr || up_scales_host == nullptr ||
+      out == nullptr) {
+    return fail(Q35B_ERR_ARGUMENT, "NVFP4 weight creation received a null buffer.");
+  }
+  *out = nullptr;
+  if (n_half <= 0 || (n_half % 8) != 0) return fail(Q35B_ERR_SHAPE, "A gate/up weight needs a row count that is a multiple of 8.");
+  if (const int st = validate_dims(2 * n_half, k, 0, 1)) return st;
+  // rows alternate in groups of eight: 8 gate rows, 8 up rows, ...
+  const size_t code_row = static_cast<size_t>(k) / 2, scale_row = static_cast<size_t>(k) / 16;
+  std::vector<uint8_t> codes(2 * static_cast<size_t>(n_half) * code_row), scales(2 * static_cast<size_t>(n_half) * scale_row);
+  for (int grp = 0; grp < n_half / 8; ++grp) {
+    std::memcpy(&codes[(2 * grp) * 8 * code_row], gate_codes_host + static_cast<size_t>(grp) * 8 * code_row, 8 * code_row);
+    std::memcpy(&codes[(2 * grp + 1) * 8 * code_row], up_codes_host + static_cast<size_t>(grp) * 8 * code_row, 8 * code_row);
+    std::memcpy(&scales[(2 * grp) * 8 * scale_row], gate_scales_host + static_cast<size_t>(grp) * 8 * scale_row, 8 * scale_row);
+    std::memcpy(&scales[(2 * grp + 1) * 8 * scale_row], up_scales_host + static_cast<size_t>(grp) * 8 * scale_row, 8 * scale_row);
+  }
+  q35b_weight * w = nullptr;
+  if (const int st = q35b_weight_create(codes.data(), scales.data(), gate_weight_scale_2, 1.0f, 2 * n_half, k, 0, 1, &w)) return st;
+  w->gate_up = true;
+  w->s2_up = up_weight_scale_2;
+  *out = w;
+  return Q35B_OK;
+}
+
+int q35b_weight_is_gate_up(const q35b_weight * w) { return (w != nullptr && w->gate_up) ? 1 : 0; }
+
+int q35b_weight_dequant_bf16(const q35b_weight * w, void * w_bf16, q35b_stream stream) {
+  return launch_dequant_bf16(w, w_bf16, static_cast<cudaStream_t>(stream));
+}
+
 void q35b_weight_destroy(q35b_weight * w) {
   if (w == nullptr) return;
   for (auto *& b : w->stream_batch) {
@@ -222,13 +255,14 @@ int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void
     }
     if (m < 1 || m > 8) return fail(Q35B_ERR_SHAPE, "NVFP4 decode projection supports 1..8 tokens.");
     if (w->rows == 0) return Q35B_OK;
+    if (w->gate_up) return fail(Q35B_ERR_ARGUMENT, "A gate/up weight runs through the projection work list (q35b_gemv_batch_*).");
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) {
       return fail(Q35B_ERR_ARGUMENT, "Activations of the streaming NVFP4 projection must be 16-byte aligned.");
     }
     auto * wm = const_cast<q35b_weight *>(w);
     if (wm->stream_batch[m] == nullptr) {
       // first use with this token count: build (and upload) the single-projection work list
-      q35b_gemv_item item{w, nullptr, nullptr};
+      q35b_gemv_item item{w, nullptr, nullptr, nullptr};
       if (const int st = gemv_batch_build(&item, 1, m, &wm->stream_batch[m])) return st;
     }
     return gemv_batch_launch(wm->stream_batch[m], x_bf16, y_bf16, static_cast<cudaStream_t>(stream));

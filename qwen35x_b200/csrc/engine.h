@@ -38,6 +38,8 @@ struct q35b_weight {
   int row_begin = 0;  // first global row of this shard
   int rows = 0;       // rows held
   float s2 = 1.0f;    // weight_scale_2
+  float s2_up = 1.0f; // weight_scale_2 of the up half of a gate/up weight
+  bool gate_up = false;  // rows alternate 8 gate / 8 up
   float input_scale = 1.0f;
   int device = 0;
   void * base = nullptr;            // the allocation
@@ -58,6 +60,7 @@ struct q35b_weight {
 namespace q35b {
 
 // gemv_w4a16.cu
+int launch_dequant_bf16(const q35b_weight * w, void * w_bf16, cudaStream_t s);
 int launch_gemv_bf16(const q35b_weight * w, const void * x_bf16, int m, void * y_bf16, int kernel, cudaStream_t s);
 int launch_gemv_f32(const q35b_weight * w, const float * x, float input_scale, float * y, int kernel, cudaStream_t s);
 

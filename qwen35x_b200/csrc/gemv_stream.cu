@@ -54,6 +54,8 @@ constexpr int kZeroHalfs = 256;                 // covers the 8 chunk offsets (3
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kXPad = 8;                        // fp16 elements of padding between tokens in shared memory
 
+enum Epilogue : int { kEpiPlain = 0, kEpiGateUp = 1 };
+
 enum StatusCode : unsigned { kProducerWait = 11, kPrepWait = 12, kConsumerWait = 13, kConsumerXWait = 14 };
 
 struct alignas(128) GemvItem {
@@ -80,6 +82,9 @@ struct alignas(16) GemvTile {
   const uint8_t * codes;         // first code byte of this row block
   const __nv_bfloat16 * x;
   __nv_bfloat16 * y;
+  const __nv_bfloat16 * residual;  // NULL or [m, rows]: added before the BF16 rounding
+  float s2_up;                     // gate/up weight: weight_scale_2 of the up rows
+  int epilogue;                    // kEpiPlain | kEpiGateUp
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -482,6 +487,9 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const int rows = tile->rows;
         const float s2 = tile->s2;
         const int row_a = tile->row_block * kTileRows + r0;
+        const __nv_bfloat16 * residual = tile->residual;
+        const bool gate_up = tile->epilogue == kEpiGateUp;
+        const float s2_up = tile->s2_up;
 #pragma unroll
         for (int ts = 0; ts < MT; ++ts) {
 #pragma unroll
@@ -491,9 +499,28 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               if (tok0 + e < m_tokens) {
-                const float unscale = xs[tok0 + e] * s2;  // undo the token's fp16 scaling, apply weight_scale_2
-                if (row_a < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a] = __float2bfloat16_rn(acc[ts][e] * unscale);
-                if (row_a + 8 < rows) y[static_cast<size_t>(tok0 + e) * rows + row_a + 8] = __float2bfloat16_rn(acc[ts][2 + e] * unscale);
+                const float unscale = xs[tok0 + e];  // undoes the token's fp16 scaling
+                if (gate_up) {
+                  // rows alternate 8 gate / 8 up: this lane's row r0 is gate row j, its row r0 + 8 the matching up row
+                  const int j = (row_a >> 4) * 8 + (row_a & 7);
+                  if (row_a + 8 < rows) {
+                    const float gate = acc[ts][e] * (unscale * s2);
+                    const float up = acc[ts][2 + e] * (unscale * s2_up);
+                    y[static_cast<size_t>(tok0 + e) * (rows >> 1) + j] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+                  }
+                } else {
+                  const float f = unscale * s2;
+                  if (row_a < rows) {
+                    const size_t o = static_cast<size_t>(tok0 + e) * rows + row_a;
+                    const float r = residual != nullptr ? __bfloat162float(residual[o]) : 0.0f;
+                    y[o] = __float2bfloat16_rn(acc[ts][e] * f + r);
+                  }
+                  if (row_a + 8 < rows) {
+                    const size_t o = static_cast<size_t>(tok0 + e) * rows + row_a + 8;
+                    const float r = residual != nullptr ? __bfloat162float(residual[o]) : 0.0f;
+                    y[o] = __float2bfloat16_rn(acc[ts][2 + e] * f + r);
+                  }
+                }
               }
             }
           }
@@ -586,6 +613,9 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
     if (w == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 projection work list holds a null weight.");
     if ((w->k % 256) != 0) return fail(Q35B_ERR_SHAPE, "The streaming NVFP4 projection needs cols to be a multiple of 256.");
     if (w->negative_scales) return fail(Q35B_ERR_FORMAT, "The streaming NVFP4 projection needs unsigned E4M3 block scales.");
+    if (w->gate_up && items[i].residual_bf16 != nullptr) {
+      return fail(Q35B_ERR_ARGUMENT, "A gate/up projection takes no residual.");
+    }
     if ((reinterpret_cast<uintptr_t>(items[i].x_bf16) & 15u) != 0) {
       return fail(Q35B_ERR_ARGUMENT, "Activations of the NVFP4 projection work list must be 16-byte aligned.");
     }
@@ -632,6 +662,9 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
       tl.codes = w->codes + static_cast<size_t>(rb) * kTileRows * (w->k / 2);
       tl.x = it.x;
       tl.y = it.y;
+      tl.residual = static_cast<const __nv_bfloat16 *>(items[i].residual_bf16);
+      tl.s2_up = w->s2_up;
+      tl.epilogue = w->gate_up ? kEpiGateUp : kEpiPlain;
       all.push_back(tl);
     }
     b->bytes_per_run += w->codes_bytes + w->scales_bytes;

@@ -181,6 +181,34 @@ gemv_w4a16_generic_kernel(const uint8_t * __restrict__ codes, const uint8_t * __
   }
 }
 
+// One thread per 16-weight block: bf16(e2m1 * (e4m3 * s2)), the reference's load-time dequantisation
+// (src/runtime/qwen35x_cuda_backend.cpp:742-755).  Rows of a gate/up weight take the scale of their half.
+__global__ void __launch_bounds__(kThreads)
+dequant_bf16_kernel(const uint8_t * __restrict__ codes, const uint8_t * __restrict__ scales, __nv_bfloat16 * __restrict__ out,
+                    int rows, int k, float s2, float s2_up, int gate_up) {
+  const int scale_cols = k >> 4;
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<size_t>(rows) * scale_cols) return;
+  const int row = static_cast<int>(idx / scale_cols);
+  const float row_s2 = (gate_up && ((row >> 3) & 1)) ? s2_up : s2;
+  const float scale = e4m3_to_f32(scales[idx]) * row_s2;
+  const uint2 cw = *reinterpret_cast<const uint2 *>(codes + idx * 8);
+  const uint32_t w[2] = {cw.x, cw.y};
+  uint32_t packed[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t c0 = (w[j >> 2] >> ((j & 3) * 8)) & 0xfu;
+    const uint32_t c1 = (w[j >> 2] >> ((j & 3) * 8 + 4)) & 0xfu;
+    const float v0 = __uint_as_float(((c0 & 7u) << 22) | ((c0 & 8u) << 28)) * 0x1p126f * scale;
+    const float v1 = __uint_as_float(((c1 & 7u) << 22) | ((c1 & 8u) << 28)) * 0x1p126f * scale;
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+    packed[j] = *reinterpret_cast<const uint32_t *>(&h);
+  }
+  uint4 * dst = reinterpret_cast<uint4 *>(out + idx * 16);
+  dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+}
+
 template <int M, typename XT, typename OT>
 int launch_simt(const q35b_weight * w, const XT * x, OT * y, float x_scale, cudaStream_t s) {
   constexpr int RW = (M <= 2) ? 2 : 1;
@@ -198,6 +226,7 @@ int launch_any(const q35b_weight * w, const XT * x, int m, OT * y, float x_scale
   if (w == nullptr || x == nullptr || y == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 projection received a null buffer.");
   if (m < 1 || m > 8) return fail(Q35B_ERR_SHAPE, "NVFP4 decode projection supports 1..8 tokens.");
   if (w->rows == 0) return Q35B_OK;
+  if (w->gate_up) return fail(Q35B_ERR_ARGUMENT, "A gate/up weight runs through the projection work list (q35b_gemv_batch_*).");
   if (kernel != Q35B_GEMV_AUTO && kernel != Q35B_GEMV_SIMT && kernel != Q35B_GEMV_STREAM) {
     return fail(Q35B_ERR_ARGUMENT, "Unknown NVFP4 projection kernel id " + std::to_string(kernel) + ".");
   }
@@ -222,6 +251,18 @@ int launch_any(const q35b_weight * w, const XT * x, int m, OT * y, float x_scale
 }
 
 }  // namespace
+
+int launch_dequant_bf16(const q35b_weight * w, void * w_bf16, cudaStream_t s) {
+  if (w == nullptr || w_bf16 == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 dequantisation received a null buffer.");
+  if ((reinterpret_cast<uintptr_t>(w_bf16) & 15u) != 0) return fail(Q35B_ERR_ARGUMENT, "NVFP4 dequantisation output must be 16-byte aligned.");
+  if (w->rows == 0) return Q35B_OK;
+  const size_t blocks16 = static_cast<size_t>(w->rows) * (w->k / 16);
+  dequant_bf16_kernel<<<static_cast<unsigned>((blocks16 + kThreads - 1) / kThreads), kThreads, 0, s>>>(
+    w->codes, w->scales, static_cast<__nv_bfloat16 *>(w_bf16), w->rows, w->k, w->s2, w->s2_up, w->gate_up ? 1 : 0);
+  count_launch();
+  Q35B_CUDA_TRY(cudaGetLastError(), "dequant_bf16_kernel launch");
+  return Q35B_OK;
+}
 
 int launch_gemv_bf16(const q35b_weight * w, const void * x_bf16, int m, void * y_bf16, int kernel, cudaStream_t s) {
   return launch_any(w, static_cast<const __nv_bfloat16 *>(x_bf16), m, static_cast<__nv_bfloat16 *>(y_bf16), 1.0f,

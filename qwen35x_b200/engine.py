@@ -39,6 +39,12 @@ def lib() -> C.CDLL:
     L.q35b_weight_create.argtypes = [vp, vp, f, f, i, i, i, i, C.POINTER(vp)]
     L.q35b_weight_create_from_device.restype = i
     L.q35b_weight_create_from_device.argtypes = [vp, vp, f, f, i, i, i, i, vp, C.POINTER(vp)]
+    L.q35b_weight_create_gate_up.restype = i
+    L.q35b_weight_create_gate_up.argtypes = [vp, vp, f, vp, vp, f, i, i, C.POINTER(vp)]
+    L.q35b_weight_is_gate_up.restype = i
+    L.q35b_weight_is_gate_up.argtypes = [vp]
+    L.q35b_weight_dequant_bf16.restype = i
+    L.q35b_weight_dequant_bf16.argtypes = [vp, vp, vp]
     L.q35b_weight_destroy.restype = None
     L.q35b_weight_destroy.argtypes = [vp]
     for name in ("q35b_weight_row_begin", "q35b_weight_rows", "q35b_weight_cols"):
@@ -132,6 +138,7 @@ class Nvfp4Weight:
         self.row_begin = L.q35b_weight_row_begin(self._h)
         self.rows = L.q35b_weight_rows(self._h)
         self.stream_bytes = int(L.q35b_weight_stream_bytes(self._h))
+        self.gate_up = bool(L.q35b_weight_is_gate_up(self._h))
 
     @classmethod
     def from_host(cls, codes: np.ndarray, scales: np.ndarray, weight_scale_2: float, input_scale: float = 1.0,
@@ -146,6 +153,26 @@ class Nvfp4Weight:
         _check(lib().q35b_weight_create(codes.ctypes.data, scales.ctypes.data, weight_scale_2, input_scale, n, k,
                                         shard_index, shard_count, C.byref(h)))
         return cls(h.value, n, k, weight_scale_2, input_scale)
+
+    @classmethod
+    def gate_up_from_host(cls, gate_codes, gate_scales, gate_s2: float, up_codes, up_scales, up_s2: float) -> "Nvfp4Weight":
+        """gate_proj + up_proj as one weight with rows alternating in groups of eight (for the fused SiLU epilogue)."""
+        _torch()
+        arrs = [np.ascontiguousarray(a, dtype=np.uint8) for a in (gate_codes, gate_scales, up_codes, up_scales)]
+        n_half, k = arrs[0].shape[0], arrs[0].shape[1] * 2
+        if arrs[2].shape != arrs[0].shape or arrs[1].shape != (n_half, k // 16) or arrs[3].shape != (n_half, k // 16):
+            raise Q35bError(2, "NVFP4 packed weight or scale size does not match matrix dimensions.")
+        h = C.c_void_p()
+        _check(lib().q35b_weight_create_gate_up(arrs[0].ctypes.data, arrs[1].ctypes.data, gate_s2, arrs[2].ctypes.data,
+                                                arrs[3].ctypes.data, up_s2, n_half, k, C.byref(h)))
+        return cls(h.value, 2 * n_half, k, gate_s2, 1.0)
+
+    def dequant_bf16(self):
+        """The whole weight as BF16 [rows, K] on the device (the reference's load-time NVFP4 -> BF16 conversion)."""
+        torch = _torch()
+        out = torch.empty((self.rows, self.k), dtype=torch.bfloat16, device="cuda")
+        _check(lib().q35b_weight_dequant_bf16(self._h, out.data_ptr(), _stream_ptr(torch)))
+        return out
 
     @classmethod
     def from_device(cls, codes, scales, weight_scale_2: float, input_scale: float = 1.0, shard_index: int = 0,
@@ -202,22 +229,29 @@ def gemv_w4a16_f32(weight: Nvfp4Weight, x, input_scale: float = 1.0, out=None, k
 
 
 class _GemvItem(C.Structure):
-    _fields_ = [("weight", C.c_void_p), ("x_bf16", C.c_void_p), ("y_bf16", C.c_void_p)]
+    _fields_ = [("weight", C.c_void_p), ("x_bf16", C.c_void_p), ("y_bf16", C.c_void_p), ("residual_bf16", C.c_void_p)]
 
 
 class GemvBatch:
     """A prepared work list of independent decode projections run by one persistent launch
-    (q35b_gemv_batch_* in include/q35b_nvfp4.h).  items: sequence of (Nvfp4Weight, x [m,K] bf16, y [m,rows] bf16);
-    the tensors must stay alive and in place for the life of the batch."""
+    (q35b_gemv_batch_* in include/q35b_nvfp4.h).  items: sequence of (Nvfp4Weight, x [m,K] bf16, y [m,out_rows] bf16)
+    or (weight, x, y, residual [m,rows] bf16): with a residual the projection is added to it before the BF16 rounding;
+    a gate/up weight (Nvfp4Weight.gate_up_from_host) yields silu(gate)*up with out_rows = rows/2.
+    The tensors must stay alive and in place for the life of the batch."""
 
     def __init__(self, items, m: int):
         torch = _torch()
         self._keep = list(items)
         arr = (_GemvItem * len(self._keep))()
-        for j, (w, x, y) in enumerate(self._keep):
+        for j, item in enumerate(self._keep):
+            w, x, y = item[0], item[1], item[2]
+            res = item[3] if len(item) > 3 else None
+            out_rows = w.rows // 2 if w.gate_up else w.rows
             assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and tuple(x.shape) == (m, w.k)
-            assert y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and tuple(y.shape) == (m, w.rows)
-            arr[j] = _GemvItem(w.handle.value, x.data_ptr(), y.data_ptr())
+            assert y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and tuple(y.shape) == (m, out_rows)
+            if res is not None:
+                assert res.is_cuda and res.dtype == torch.bfloat16 and res.is_contiguous() and tuple(res.shape) == (m, w.rows)
+            arr[j] = _GemvItem(w.handle.value, x.data_ptr(), y.data_ptr(), res.data_ptr() if res is not None else None)
         h = C.c_void_p()
         _check(lib().q35b_gemv_batch_create(arr, len(self._keep), m, C.byref(h)))
         self._h = h

@@ -1,0 +1,102 @@
+"""Fused epilogues of the decode work list and the NVFP4 -> BF16 weight dequantisation, against the CPU oracle.
+Tolerance: relative L2 <= 1e-3 (BF16 outputs)."""
+import numpy as np
+import pytest
+
+from helpers import from_torch_bf16, make_activations, make_weight, to_torch_bf16
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-3
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_projection_plus_residual(engine, oracle, m):
+    """y = bf16(projection + residual): matvec_down_residual_nvfp4 (src/kernels/cuda/decode_layers.cuh:404-428)."""
+    import torch
+
+    n, k = 1024, 3584
+    _, codes, scales, s2 = make_weight(n, k, seed=11)
+    xb = make_activations(m, k, seed=12)
+    rb = make_activations(m, n, seed=13)
+    w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+    y = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    batch = engine.GemvBatch([(w, to_torch_bf16(xb), y, to_torch_bf16(rb))], m)
+    batch.run()
+    torch.cuda.synchronize()
+    assert batch.status() == 0
+    _, yf = oracle.gemv_bf16(codes, scales, s2, xb, threads=8)
+    exp = oracle.bf16_round(yf + oracle.bf16_to_f32(rb))
+    got = from_torch_bf16(y)
+    assert oracle.rel_l2(oracle.bf16_to_f32(got), oracle.bf16_to_f32(exp)) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("m", [1, 2, 5])
+def test_gate_up_silu(engine, oracle, m):
+    """y = bf16(silu(gate . x) * (up . x)), silu(g) = g / (1 + exp(-g)): matvec_gate_up_silu_nvfp4
+    (decode_layers.cuh:339-365) with the exact sigmoid of silu_multiply_kernel (src/runtime/cuda_bench.cu:215-222)."""
+    import torch
+
+    n_half, k = 3584, 1024
+    _, g_codes, g_scales, g_s2 = make_weight(n_half, k, seed=21, std=0.05)
+    _, u_codes, u_scales, u_s2 = make_weight(n_half, k, seed=22, std=0.03)
+    xb = make_activations(m, k, seed=23)
+    w = engine.Nvfp4Weight.gate_up_from_host(g_codes, g_scales, g_s2, u_codes, u_scales, u_s2)
+    assert w.gate_up and w.rows == 2 * n_half
+    y = torch.zeros((m, n_half), dtype=torch.bfloat16, device="cuda")
+    batch = engine.GemvBatch([(w, to_torch_bf16(xb), y)], m)
+    batch.run()
+    torch.cuda.synchronize()
+    assert batch.status() == 0
+    _, gate = oracle.gemv_bf16(g_codes, g_scales, g_s2, xb, threads=8)
+    _, up = oracle.gemv_bf16(u_codes, u_scales, u_s2, xb, threads=8)
+    exp = (gate / (np.float32(1.0) + np.exp(-gate, dtype=np.float32)) * up).astype(np.float32)
+    got = oracle.bf16_to_f32(from_torch_bf16(y))
+    assert oracle.rel_l2(got, oracle.bf16_to_f32(oracle.bf16_round(exp))) <= REL_L2_TOL
+    # a gate/up weight is only meaningful with its epilogue
+    with pytest.raises(engine.Q35bError):
+        engine.gemv_w4a16(w, to_torch_bf16(xb))
+
+
+def test_mlp_work_list(engine, oracle):
+    """gate+up+SiLU and an independent down+residual in one launch, mixed with a plain projection."""
+    import torch
+
+    k, inter = 1024, 512
+    _, g_codes, g_scales, g_s2 = make_weight(inter, k, seed=31)
+    _, u_codes, u_scales, u_s2 = make_weight(inter, k, seed=32)
+    _, d_codes, d_scales, d_s2 = make_weight(k, inter * 2, seed=33)
+    x1 = make_activations(2, k, 34)
+    x2 = make_activations(2, inter * 2, 35)
+    res = make_activations(2, k, 36)
+    gu = engine.Nvfp4Weight.gate_up_from_host(g_codes, g_scales, g_s2, u_codes, u_scales, u_s2)
+    down = engine.Nvfp4Weight.from_host(d_codes, d_scales, d_s2)
+    y1 = torch.zeros((2, inter), dtype=torch.bfloat16, device="cuda")
+    y2 = torch.zeros((2, k), dtype=torch.bfloat16, device="cuda")
+    y3 = torch.zeros((2, k), dtype=torch.bfloat16, device="cuda")
+    batch = engine.GemvBatch([(gu, to_torch_bf16(x1), y1), (down, to_torch_bf16(x2), y2, to_torch_bf16(res)),
+                              (down, to_torch_bf16(x2), y3)], 2)
+    batch.run()
+    torch.cuda.synchronize()
+    assert batch.status() == 0
+    _, gate = oracle.gemv_bf16(g_codes, g_scales, g_s2, x1, threads=8)
+    _, up = oracle.gemv_bf16(u_codes, u_scales, u_s2, x1, threads=8)
+    e1 = oracle.bf16_round((gate / (1 + np.exp(-gate)) * up).astype(np.float32))
+    eb, ef = oracle.gemv_bf16(d_codes, d_scales, d_s2, x2, threads=8)
+    e2 = oracle.bf16_round(ef + oracle.bf16_to_f32(res))
+    for got, exp in ((y1, e1), (y2, e2), (y3, eb)):
+        assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(got)), oracle.bf16_to_f32(exp)) <= REL_L2_TOL
+
+
+def test_weight_dequant_bf16_bit_exact(engine, oracle):
+    """bf16(e2m1 * (e4m3 * s2)) per element, bit-exact with the oracle's restatement of
+    src/runtime/qwen35x_cuda_backend.cpp:742-755; all codes and (non-negative and negative) scale bytes."""
+    rng = np.random.default_rng(2)
+    n, k = 130, 512
+    codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    scales = rng.integers(0, 256, size=(n, k // 16), dtype=np.uint8)
+    s2 = 3.0e-4
+    w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+    got = from_torch_bf16(w.dequant_bf16())
+    exp = oracle.dequant_weights_bf16(codes, scales, s2)
+    assert np.array_equal(got, exp)
