@@ -198,6 +198,15 @@ Q35B_API int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes,
                                  const float * input_scale_dev, int m, void * c_bf16, int ldc,
                                  unsigned int * status_dev, q35b_stream stream);
 
+/* Same GEMM with the residual add fused into the epilogue: c = bf16(projection + residual), residual [m, rows] BF16
+ * with row stride ldr.  Replaces pf_add_residual_bf16 after the down / o projections
+ * (src/kernels/cuda/prefill.cu:679, pf_mlp_chunked :647-680).
+ * On a gate/up weight (q35b_weight_create_gate_up) q35b_gemm_w4a4_bf16 itself ends with silu(gate) * up and writes
+ * c [m, rows/2], replacing pf_silu_mul_bf16 (src/kernels/cuda/prefill.cu:674-678). */
+Q35B_API int q35b_gemm_w4a4_bf16_residual(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
+                                          const float * input_scale_dev, int m, const void * residual_bf16, int ldr,
+                                          void * c_bf16, int ldc, unsigned int * status_dev, q35b_stream stream);
+
 /* Prefill projection for callers that cannot allocate device memory (no counterpart in the reference, whose
  * bridges all take caller-allocated scratch, include/qwen35x/runtime/cuda_bench.h:70-83).
  *

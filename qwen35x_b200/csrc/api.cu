@@ -319,8 +319,16 @@ int q35b_quantize_weight_f32(const float * w_f32, int n, int k, uint8_t * codes,
 int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
                         const float * input_scale_dev, int m, void * c_bf16, int ldc, unsigned int * status_dev,
                         q35b_stream stream) {
-  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, c_bf16, ldc,
+  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, c_bf16, ldc, nullptr, 0,
                           status_dev, static_cast<cudaStream_t>(stream));
+}
+
+int q35b_gemm_w4a4_bf16_residual(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
+                                 const float * input_scale_dev, int m, const void * residual_bf16, int ldr, void * c_bf16,
+                                 int ldc, unsigned int * status_dev, q35b_stream stream) {
+  if (residual_bf16 == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection received a null residual.");
+  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, c_bf16, ldc,
+                          residual_bf16, ldr, status_dev, static_cast<cudaStream_t>(stream));
 }
 
 /* Host-callable twins of the device encoders/decoders, so that their

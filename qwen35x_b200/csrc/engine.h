@@ -85,12 +85,15 @@ size_t gemv_batch_bytes(const struct q35b_gemv_batch * b);
 // gemm_w4a4_tcgen05.cu
 int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, int box_rows);
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
-                     int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s);
+                     int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
+                     cudaStream_t s);
 
 
 // gemm_w4a4_2cta.cu
 bool gemm_2cta_eligible(const q35b_weight * w, int m);
+struct GemmEpilogue;
 int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
-                          int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s);
+                          int m, void * c_bf16, int ldc, const GemmEpilogue & ep, unsigned int * status_dev,
+                          cudaStream_t s);
 
 }  // namespace q35b

@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 
 #include "engine.h"
+#include "gemm_epilogue.cuh"
 #include "nvfp4_codec.cuh"
 
 namespace q35b {
@@ -160,7 +161,7 @@ __device__ __forceinline__ void cluster_sync() {
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                      const float * __restrict__ g_dev, float s2, int m, int n, int k_bytes, int m_tiles, int num_tiles,
+                      const float * __restrict__ g_dev, const GemmEpilogue ep, int m, int n, int k_bytes, int m_tiles, int num_tiles,
                       __nv_bfloat16 * __restrict__ c, int ldc, unsigned int * status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -306,7 +307,7 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else {
     // ---------------- epilogue (both CTAs): this CTA's 128 rows of the pair's tile ----------------
     const int quarter = warp & 3;
-    const float alpha = __ldg(g_dev) * s2;
+    const float g = __ldg(g_dev);
     uint32_t li = 0;
     bool ok = !aborted;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
@@ -321,8 +322,6 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = tm * kTileM + static_cast<int>(rank) * kCtaRows + quarter * 32 + lane;
       const uint32_t taddr = tmem_acc + ab * kTileN + (static_cast<uint32_t>(quarter * 32) << 16);
-      __nv_bfloat16 * crow = c + static_cast<size_t>(row) * ldc + static_cast<size_t>(tn) * kTileN;
-      const int n_left = n - tn * kTileN;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTileN; c0 += 32) {
         uint32_t r[32];
@@ -334,28 +333,7 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + ab), 0);
         }
-        if (row < m) {
-          if (c0 + 32 <= n_left && ((reinterpret_cast<uintptr_t>(crow + c0) & 31u) == 0)) {
-            // 32 columns = 64 bytes per row: two 256-bit stores, each a whole 32-byte sector
-#pragma unroll
-            for (int v = 0; v < 2; ++v) {
-              uint32_t p[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 16 + e * 2]) * alpha,
-                                                               __uint_as_float(r[v * 16 + e * 2 + 1]) * alpha);
-                p[e] = *reinterpret_cast<const uint32_t *>(&h);
-              }
-              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(crow + c0 + v * 16), "r"(p[0]),
-                           "r"(p[1]), "r"(p[2]), "r"(p[3]), "r"(p[4]), "r"(p[5]), "r"(p[6]), "r"(p[7])
-                           : "memory");
-            }
-          } else {
-            for (int e = 0; e < 32; ++e) {
-              if (c0 + e < n_left) crow[c0 + e] = __float2bfloat16_rn(__uint_as_float(r[e]) * alpha);
-            }
-          }
-        }
+        if (row < m) gemm_store_chunk32(r, row, tn * kTileN + c0, n, g, ep, c, ldc);
       }
     }
   }
@@ -404,7 +382,8 @@ bool gemm_2cta_eligible(const q35b_weight * w, int m) {
 }
 
 int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
-                          int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s) {
+                          int m, void * c_bf16, int ldc, const GemmEpilogue & ep, unsigned int * status_dev,
+                          cudaStream_t s) {
   static bool attr_set[64] = {false};
   if (!attr_set[w->device & 63]) {
     Q35B_CUDA_TRY(cudaFuncSetAttribute(gemm_w4a4_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
@@ -424,7 +403,7 @@ int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_
   const int n_tiles = (w->rows + kTileN - 1) / kTileN;
   const int num_tiles = m_tiles * n_tiles;
   const int pairs = std::max(1, std::min(num_tiles, sm_count() / 2));
-  gemm_w4a4_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, s>>>(tmap_a, w->tmap2_codes, tmap_sfa, w->tmap2_sf, g_dev, w->s2, m,
+  gemm_w4a4_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, s>>>(tmap_a, w->tmap2_codes, tmap_sfa, w->tmap2_sf, g_dev, ep, m,
                                                                w->rows, w->k / 2, m_tiles, num_tiles,
                                                                static_cast<__nv_bfloat16 *>(c_bf16), ldc, status_dev);
   count_launch();

@@ -27,6 +27,7 @@
 #include <mutex>
 
 #include "engine.h"
+#include "gemm_epilogue.cuh"
 #include "nvfp4_codec.cuh"
 
 namespace q35b {
@@ -184,7 +185,7 @@ template <int BLOCK_N>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const uint8_t * __restrict__ sfa, const uint8_t * __restrict__ sfb,
-                         const float * __restrict__ g_dev, float s2, int m, int n, int k_bytes,
+                         const float * __restrict__ g_dev, const GemmEpilogue ep, int m, int n, int k_bytes,
                          int sfb_row_blocks, __nv_bfloat16 * __restrict__ c, int ldc, unsigned int * status) {
   using C = Cfg<BLOCK_N>;
   extern __shared__ uint8_t smem_raw[];
@@ -311,34 +312,14 @@ gemm_w4a4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (lane == 0) atomicExch(status, kStatusEpilogueWait);
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float alpha = __ldg(g_dev) * s2;
+      const float g = __ldg(g_dev);
       const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
-      __nv_bfloat16 * crow = c + static_cast<size_t>(row) * ldc + static_cast<size_t>(tile_n) * BLOCK_N;
-      const int n_left = n - tile_n * BLOCK_N;
 #pragma unroll 1
       for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < m) {
-          if (c0 + 32 <= n_left && ((reinterpret_cast<uintptr_t>(crow + c0) & 15u) == 0)) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t p[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + e * 2]) * alpha,
-                                                               __uint_as_float(r[v * 8 + e * 2 + 1]) * alpha);
-                p[e] = *reinterpret_cast<const uint32_t *>(&h);
-              }
-              *reinterpret_cast<uint4 *>(crow + c0 + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
-            }
-          } else {
-            for (int e = 0; e < 32; ++e) {
-              if (c0 + e < n_left) crow[c0 + e] = __float2bfloat16_rn(__uint_as_float(r[e]) * alpha);
-            }
-          }
-        }
+        if (row < m) gemm_store_chunk32(r, row, tile_n * BLOCK_N + c0, n, g, ep, c, ldc);
       }
     }
   }
@@ -396,7 +377,7 @@ namespace {
 
 template <int BLOCK_N>
 int launch_tile(q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_scales, const float * g_dev, int m,
-                void * c, int ldc, unsigned int * status, cudaStream_t s) {
+                void * c, int ldc, const GemmEpilogue & ep, unsigned int * status, cudaStream_t s) {
   using C = Cfg<BLOCK_N>;
   static bool attr_set[64] = {false};
   auto kernel = gemm_w4a4_tcgen05_kernel<BLOCK_N>;
@@ -411,7 +392,7 @@ int launch_tile(q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_s
     w->tmap_block_n = BLOCK_N;
   }
   const dim3 grid((w->rows + BLOCK_N - 1) / BLOCK_N, (m + kBlockM - 1) / kBlockM);
-  kernel<<<grid, kThreads, C::kSmemBytes, s>>>(tmap_a, w->tmap_codes, a_scales, w->scales_tiled, g_dev, w->s2, m,
+  kernel<<<grid, kThreads, C::kSmemBytes, s>>>(tmap_a, w->tmap_codes, a_scales, w->scales_tiled, g_dev, ep, m,
                                                w->rows, w->k / 2, (w->rows + 127) / 128,
                                                static_cast<__nv_bfloat16 *>(c), ldc, status);
   count_launch();
@@ -422,11 +403,22 @@ int launch_tile(q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_s
 }  // namespace
 
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
-                     int m, void * c_bf16, int ldc, unsigned int * status_dev, cudaStream_t s) {
+                     int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
+                     cudaStream_t s) {
   if (w == nullptr || a_codes == nullptr || a_scales_tiled == nullptr || g_dev == nullptr || c_bf16 == nullptr) {
     return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection received a null device buffer.");
   }
-  if (m <= 0 || ldc < w->rows) return fail(Q35B_ERR_SHAPE, "Invalid dimensions for NVFP4 prefill projection.");
+  const int out_cols = w->gate_up ? w->rows / 2 : w->rows;
+  if (m <= 0 || ldc < out_cols) return fail(Q35B_ERR_SHAPE, "Invalid dimensions for NVFP4 prefill projection.");
+  if (residual_bf16 != nullptr && (w->gate_up || ldr < w->rows)) {
+    return fail(Q35B_ERR_ARGUMENT, "Invalid residual for NVFP4 prefill projection.");
+  }
+  GemmEpilogue ep;
+  ep.s2 = w->s2;
+  ep.s2_up = w->s2_up;
+  ep.gate_up = w->gate_up ? 1 : 0;
+  ep.residual = static_cast<const __nv_bfloat16 *>(residual_bf16);
+  ep.ldr = ldr;
   if ((w->k % 64) != 0) return fail(Q35B_ERR_SHAPE, "NVFP4 W4A4 GEMM needs cols to be a multiple of 64.");
   if ((reinterpret_cast<uintptr_t>(a_codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a_scales_tiled) & 15u) != 0) {
     return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection buffers must be 16-byte aligned.");
@@ -444,16 +436,16 @@ int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a
   }
   // Large problems: pairs of CTAs on 256 x 256 tiles, persistent (gemm_w4a4_2cta.cu).
   if (gemm_2cta_eligible(w, m)) {
-    return launch_gemm_w4a4_2cta(w, a_codes, a_scales_tiled, g_dev, m, c_bf16, ldc, status_dev, s);
+    return launch_gemm_w4a4_2cta(w, a_codes, a_scales_tiled, g_dev, m, c_bf16, ldc, ep, status_dev, s);
   }
   CUtensorMap tmap_a;
   if (const int st = make_code_map(&tmap_a, a_codes, m, w->k / 2, kBlockM)) return st;
   // Small problems get narrower tiles so that more SMs have work.
   const long tiles256 = static_cast<long>((w->rows + 255) / 256) * ((m + 127) / 128);
   if (tiles256 >= sm_count() || w->rows <= 128) {
-    if (w->rows > 128) return launch_tile<256>(w, tmap_a, a_scales_tiled, g_dev, m, c_bf16, ldc, status_dev, s);
+    if (w->rows > 128) return launch_tile<256>(w, tmap_a, a_scales_tiled, g_dev, m, c_bf16, ldc, ep, status_dev, s);
   }
-  return launch_tile<128>(w, tmap_a, a_scales_tiled, g_dev, m, c_bf16, ldc, status_dev, s);
+  return launch_tile<128>(w, tmap_a, a_scales_tiled, g_dev, m, c_bf16, ldc, ep, status_dev, s);
 }
 
 }  // namespace q35b

@@ -82,7 +82,7 @@ int q35b_project_prefill_bf16_static(const q35b_weight * w, const void * x_bf16,
   uint8_t * codes = base + kControlBytes;
   uint8_t * scales = codes + codes_bytes;
   if (const int st = launch_quantize_bf16(x_bf16, m, w->k, global_scale, codes, scales, g_dev, workspace, s)) return st;
-  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), codes, scales, g_dev, m, c_bf16, ldc, status, s);
+  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), codes, scales, g_dev, m, c_bf16, ldc, nullptr, 0, status, s);
 }
 
 }  // extern "C"

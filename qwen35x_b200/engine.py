@@ -84,6 +84,8 @@ def lib() -> C.CDLL:
     L.q35b_static_prefill_capacity_bytes.restype = sz
     L.q35b_project_prefill_bf16_static.restype = i
     L.q35b_project_prefill_bf16_static.argtypes = [vp, vp, i, f, vp, i, vp]
+    L.q35b_gemm_w4a4_bf16_residual.restype = i
+    L.q35b_gemm_w4a4_bf16_residual.argtypes = [vp, vp, vp, vp, i, vp, i, vp, i, vp, vp]
     L.q35b_debug_encode_ue4m3.restype = C.c_uint8
     L.q35b_debug_encode_ue4m3.argtypes = [f]
     L.q35b_debug_encode_e2m1.restype = C.c_uint8
@@ -336,22 +338,30 @@ def quantize_weight(w_f32):
     return codes, scales, float(s2.item())
 
 
-def gemm_w4a4(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, out=None, status=None):
-    """Prefill projection on quantised activations: -> c [m, rows] bf16."""
+def gemm_w4a4(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, out=None, status=None, residual=None):
+    """Prefill projection on quantised activations: -> c [m, rows] bf16; with `residual` [m, rows] bf16 the sum is
+    rounded once; a gate/up weight gives silu(gate) * up, [m, rows/2]."""
     torch = _torch()
+    out_cols = weight.rows // 2 if weight.gate_up else weight.rows
     if out is None:
-        out = torch.empty((m, weight.rows), dtype=torch.bfloat16, device=a_codes.device)
+        out = torch.empty((m, out_cols), dtype=torch.bfloat16, device=a_codes.device)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
-    _check(lib().q35b_gemm_w4a4_bf16(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(), g.data_ptr(), m,
-                                     out.data_ptr(), out.stride(0), status.data_ptr() if status is not None else None,
-                                     _stream_ptr(torch)))
+    st = status.data_ptr() if status is not None else None
+    if residual is None:
+        _check(lib().q35b_gemm_w4a4_bf16(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(), g.data_ptr(), m,
+                                         out.data_ptr(), out.stride(0), st, _stream_ptr(torch)))
+    else:
+        assert residual.dtype == torch.bfloat16 and residual.stride(1) == 1 and tuple(residual.shape) == (m, weight.rows)
+        _check(lib().q35b_gemm_w4a4_bf16_residual(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(),
+                                                  g.data_ptr(), m, residual.data_ptr(), residual.stride(0),
+                                                  out.data_ptr(), out.stride(0), st, _stream_ptr(torch)))
     return out
 
 
-def project_prefill(weight: Nvfp4Weight, x, out=None, scratch=None, global_scale: float = 0.0):
-    """BF16 [m, K] -> BF16 [m, rows]: activation quantisation followed by the W4A4 GEMM."""
+def project_prefill(weight: Nvfp4Weight, x, out=None, scratch=None, global_scale: float = 0.0, residual=None):
+    """BF16 [m, K] -> BF16 [m, rows]: activation quantisation followed by the W4A4 GEMM (and its fused epilogue)."""
     codes, scales, g = quantize_activations(x, global_scale, scratch)
-    return gemm_w4a4(weight, codes, scales, g, x.shape[0], out)
+    return gemm_w4a4(weight, codes, scales, g, x.shape[0], out, residual=residual)
 
 
 def project_prefill_static(weight: Nvfp4Weight, x, out=None, global_scale: float = 0.0):

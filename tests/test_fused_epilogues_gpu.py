@@ -100,3 +100,51 @@ def test_weight_dequant_bf16_bit_exact(engine, oracle):
     got = from_torch_bf16(w.dequant_bf16())
     exp = oracle.dequant_weights_bf16(codes, scales, s2)
     assert np.array_equal(got, exp)
+
+
+@pytest.mark.parametrize("m", [7, 300])
+def test_prefill_gemm_plus_residual(engine, oracle, m):
+    """c = bf16(W4A4 projection + residual) in the GEMM epilogue (1-CTA kernel for m = 7, 2-CTA for m = 300)."""
+    import torch
+
+    n, k = 520, 1024
+    _, codes, scales, s2 = make_weight(n, k, seed=41)
+    xb = make_activations(m, k, seed=42, outlier_frac=0.001)
+    rb = make_activations(m, n, seed=43)
+    w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a_codes, a_scales, g = engine.quantize_activations(to_torch_bf16(xb))
+    c = engine.gemm_w4a4(w, a_codes, a_scales, g, m, status=status, residual=to_torch_bf16(rb))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    e_codes, e_scales, e_g = oracle.quantize_nvfp4(xb)
+    _, cf = oracle.gemm_w4a4(codes, scales, s2, e_codes, e_scales, e_g, threads=8)
+    exp = oracle.bf16_round(cf + oracle.bf16_to_f32(rb))
+    assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(c)), oracle.bf16_to_f32(exp)) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("m,n_half", [(5, 256), (300, 1000), (256, 9216)])
+def test_prefill_gate_up_silu(engine, oracle, m, n_half):
+    """c = bf16(silu(gate) * up) straight from the GEMM epilogue, [m, n_half] (half the output bytes)."""
+    import torch
+
+    k = 512 if n_half > 2000 else 1024
+    _, g_codes, g_scales, g_s2 = make_weight(n_half, k, seed=51, std=0.05)
+    _, u_codes, u_scales, u_s2 = make_weight(n_half, k, seed=52, std=0.03)
+    xb = make_activations(m, k, seed=53, outlier_frac=0.001)
+    w = engine.Nvfp4Weight.gate_up_from_host(g_codes, g_scales, g_s2, u_codes, u_scales, u_s2)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = engine.project_prefill(w, to_torch_bf16(xb))
+    a_codes, a_scales, g = engine.quantize_activations(to_torch_bf16(xb))
+    c2 = engine.gemm_w4a4(w, a_codes, a_scales, g, m, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and tuple(c.shape) == (m, n_half) and torch.equal(c, c2)
+    e_codes, e_scales, e_g = oracle.quantize_nvfp4(xb)
+    rows = np.arange(n_half) if n_half <= 1000 else np.sort(np.random.default_rng(0).choice(n_half, 64, replace=False))
+    got = oracle.bf16_to_f32(from_torch_bf16(c))[:, rows]
+    exp = np.zeros((m, len(rows)), dtype=np.float32)
+    for j, r in enumerate(rows):
+        _, gate = oracle.gemm_w4a4(g_codes[r:r + 1], g_scales[r:r + 1], g_s2, e_codes, e_scales, e_g, threads=8)
+        _, up = oracle.gemm_w4a4(u_codes[r:r + 1], u_scales[r:r + 1], u_s2, e_codes, e_scales, e_g, threads=8)
+        exp[:, j] = (gate / (1 + np.exp(-gate)) * up)[:, 0]
+    assert oracle.rel_l2(got, oracle.bf16_to_f32(oracle.bf16_round(exp))) <= REL_L2_TOL
