@@ -50,9 +50,10 @@ constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 
 constexpr int kMaxTilesInSmem = 64;             // tile descriptors staged per CTA
 constexpr int kMaxStages = 8;
 constexpr int kMaxRawDepth = 4;
-constexpr int kZeroHalfs = 256;                 // covers the 8 chunk offsets (32 halfs apart) of a K step
+constexpr int kZeroHalfs = 320;                 // covers the 8 chunk offsets (32 halfs apart) of a K step + a bank shift
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr int kXPad = 8;                        // fp16 elements of padding between tokens in shared memory
+constexpr int kXPad = 16;                       // fp16 elements of padding between tokens: consecutive tokens sit 32 bytes
+                                                // apart modulo the 128-byte bank window, so a B-fragment load has no conflict
 
 enum Epilogue : int { kEpiPlain = 0, kEpiGateUp = 1 };
 
@@ -176,10 +177,10 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   // integer round trip) keeps every later access a shared-memory access for the compiler.
   uint8_t * ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __half * xbuf = reinterpret_cast<__half *>(ring + stages * kStageBytes);        // x_bufs (1 or 2) buffers of x_buf_halfs
-  float * xsbuf = reinterpret_cast<float *>(xbuf + x_bufs * x_buf_halfs);          // 2 buffers of xs_buf_floats (1/scale)
+  __half * zeros = xbuf + x_bufs * x_buf_halfs;                                   // kZeroHalfs of 0.0, 128-byte aligned
+  float * xsbuf = reinterpret_cast<float *>(zeros + kZeroHalfs);                   // 2 buffers of xs_buf_floats (1/scale)
   float * red = xsbuf + 2 * xs_buf_floats;                                         // 2 x [8 row groups][32 lanes][4*MT]
-  __half * zeros = reinterpret_cast<__half *>(red + 2 * kRowGroups * 32 * 4 * MT);    // kZeroHalfs of 0.0
-  GemvTile * stile = reinterpret_cast<GemvTile *>(zeros + kZeroHalfs);
+  GemvTile * stile = reinterpret_cast<GemvTile *>(red + 2 * kRowGroups * 32 * 4 * MT);
   uint8_t * xraw = reinterpret_cast<uint8_t *>(stile + kMaxTilesInSmem);           // x_raw_depth buffers of x_raw_bytes
   uint64_t * bars = reinterpret_cast<uint64_t *>(xraw + static_cast<size_t>(x_raw_depth) * x_raw_bytes);
   // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2], red_full[2], red_free[2], xraw_full[kMaxRawDepth]
@@ -355,6 +356,10 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     const int r0 = 16 * rg + g;
     const int sc_off0 = (r0 & 31) * 16 + (r0 >> 5) * 4;
     const int x_lane_off = 16 * hB + 8 * (t & 1);
+    // The eight lanes served together by a 128-bit load hold two tokens of one block half: their activations fill a
+    // 64-byte window of the 128-byte bank span (buffers are 128-byte aligned, tokens 32 bytes apart modulo 128).
+    // Lanes that must feed zeros read them from the other 64 bytes of the span.
+    const __half * zsrc = zeros + (m_tokens == 1 ? 48 : ((64 * (mB >> 1) + 32 * hB + 64) & 127) >> 1);
 
     int stage = 0;
     uint32_t phase = 0;
@@ -397,7 +402,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       for (int ts = 0; ts < MT; ++ts) {
         const int token = 4 * ts + mB;
         const bool owner = b_owner && token < m_tokens;
-        bsrc[ts] = owner ? xb + static_cast<size_t>(token) * xstride + x_lane_off : zeros;
+        bsrc[ts] = owner ? xb + static_cast<size_t>(token) * xstride + x_lane_off : zsrc;
         bstep[ts] = owner ? 256 : 0;
       }
       for (int ks = 0; ks < k_steps; ++ks) {
@@ -550,7 +555,7 @@ struct Plan {
 // Shared-memory plan for a batch with at most max_k columns: two activation buffers, then as many ring stages as fit.
 bool make_plan(int m, int max_k, Plan * p) {
   const int mt = m <= 4 ? 1 : 2;
-  const int x_halfs = ((m * (max_k + kXPad) + 7) / 8) * 8;
+  const int x_halfs = ((m * (max_k + kXPad) + 63) / 64) * 64;  // whole 128-byte bank spans
   const int xs_floats = 8;
   const int raw_bytes = ((m * max_k * 2 + 127) / 128) * 128;
   const int base = 1024 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
