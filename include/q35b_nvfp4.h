@@ -58,7 +58,8 @@ typedef void * q35b_stream;
  * --nvfp4-projection-kernel accepts map onto these (reference:
  * src/runtime/runtime.cpp:378-390, values 0..3 are the reference's). */
 typedef enum q35b_gemv_kernel {
-  Q35B_GEMV_AUTO = -1,
+  Q35B_GEMV_AUTO = -1,  /* STREAM for a weight of 24 MiB or more that it can take (unless that would allocate on a
+                         * capturing stream), else SIMT */
   Q35B_GEMV_SIMT = 10,  /* 128-bit loads, in-register dequant, fp32 FMA, warp-shuffle reduction */
   Q35B_GEMV_STREAM = 11 /* persistent, TMA-fed shared-memory ring; first use per (weight, m) allocates its work list */
 } q35b_gemv_kernel;

@@ -87,6 +87,10 @@ int alloc_weight(int n, int k, int shard_index, int shard_count, float s2, float
 
 using namespace q35b;
 
+// Q35B_GEMV_AUTO sends a single projection to the streaming kernel from this many weight bytes on (measured
+// crossover on B200: the SIMT launch wins at 13 MB, the streaming kernel at 47 MB).
+static constexpr size_t kAutoStreamBytes = 24u << 20;
+
 extern "C" {
 
 const char * q35b_last_error(void) { return t_error.c_str(); }
@@ -249,6 +253,19 @@ size_t q35b_weight_stream_bytes(const q35b_weight * w) { return w ? w->codes_byt
 
 int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void * y_bf16, int kernel,
                          q35b_stream stream) {
+  if (kernel == Q35B_GEMV_AUTO && w != nullptr && m >= 1 && m <= 8 && !w->gate_up &&
+      w->codes_bytes + w->scales_bytes >= kAutoStreamBytes && x_bf16 != nullptr &&
+      (reinterpret_cast<uintptr_t>(x_bf16) & 15u) == 0 && gemv_stream_eligible(w, m)) {
+    // A weight this large keeps the persistent streaming kernel busy for longer than its set-up costs; below the
+    // threshold the plain SIMT launch finishes first.  The streaming kernel's first use allocates its work list,
+    // which a capturing stream must not do: stay on the SIMT kernel then.
+    bool can_stream = w->stream_batch[m] != nullptr;
+    if (!can_stream) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      can_stream = cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone;
+    }
+    if (can_stream) kernel = Q35B_GEMV_STREAM;
+  }
   if (kernel == Q35B_GEMV_STREAM) {
     if (w == nullptr || x_bf16 == nullptr || y_bf16 == nullptr) {
       return fail(Q35B_ERR_ARGUMENT, "NVFP4 projection received a null buffer.");

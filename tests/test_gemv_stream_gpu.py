@@ -88,3 +88,37 @@ def test_ineligible_shapes_are_rejected(engine):
     with pytest.raises(engine.Q35bError) as e:
         engine.gemv_w4a16(w2, torch.zeros((1, 256), dtype=torch.bfloat16, device="cuda"), kernel=engine.GEMV_STREAM)
     assert e.value.status == 5
+
+
+def test_auto_selection(engine, oracle):
+    """AUTO runs the streaming kernel for a weight of 24 MiB or more and the SIMT kernel below that; on a capturing
+    stream it never allocates (first use of the streaming kernel would), so it stays on the SIMT kernel there."""
+    import torch
+
+    n, k = 20480, 4096  # 47 MB of codes + scales
+    _, codes, scales, s2 = make_weight(n, k, seed=11)
+    xb = make_activations(2, k, seed=12)
+    x = to_torch_bf16(xb)
+    w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+    # capture before the streaming work list exists: must succeed (SIMT) and replay correctly
+    y_graph = torch.empty((2, n), dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            engine.gemv_w4a16(w, x, out=y_graph, kernel=engine.GEMV_AUTO)
+        graph.replay()
+        stream.synchronize()
+    y_simt = engine.gemv_w4a16(w, x, kernel=engine.GEMV_SIMT)
+    assert np.array_equal(from_torch_bf16(y_graph), from_torch_bf16(y_simt))
+    # outside a capture the large weight goes to the streaming kernel
+    y_auto = engine.gemv_w4a16(w, x, kernel=engine.GEMV_AUTO)
+    y_stream = engine.gemv_w4a16(w, x, kernel=engine.GEMV_STREAM)
+    assert np.array_equal(from_torch_bf16(y_auto), from_torch_bf16(y_stream))
+    _compare(oracle, from_torch_bf16(y_auto), codes, scales, s2, xb)
+    # a small weight stays on the SIMT kernel
+    _, c2, sc2, s22 = make_weight(3584, 1024, seed=13)
+    x2 = to_torch_bf16(make_activations(1, 1024, seed=14))
+    w2 = engine.Nvfp4Weight.from_host(c2, sc2, s22)
+    assert np.array_equal(from_torch_bf16(engine.gemv_w4a16(w2, x2, kernel=engine.GEMV_AUTO)),
+                          from_torch_bf16(engine.gemv_w4a16(w2, x2, kernel=engine.GEMV_SIMT)))
