@@ -208,6 +208,19 @@ Q35B_API int q35b_gemm_w4a4_bf16_residual(const q35b_weight * w, const uint8_t *
                                           const float * input_scale_dev, int m, const void * residual_bf16, int ldr,
                                           void * c_bf16, int ldc, unsigned int * status_dev, q35b_stream stream);
 
+/* Gate/up GEMM whose epilogue writes silu(gate) * up as an NVFP4 activation (codes [m, rows/4] bytes, tiled block
+ * scales sized by q35b_act_scales_bytes(m, rows/2)), ready to be the A operand of the down projection's
+ * q35b_gemm_w4a4_bf16(_residual) with out_scale_dev as its input_scale_dev.  Replaces pf_silu_mul_bf16 plus the
+ * quantise pass between the reference's gate/up and down GEMMs (src/kernels/cuda/prefill.cu:674-678,
+ * src/runtime/cuda_bench.cu:2621-2660).  out_scale_dev is that activation's per-tensor scale and must be known
+ * in advance (the checkpoint's input_scale of the down projection, or amax / 2688 from a calibration run); values
+ * beyond 2688 * scale saturate.  The bits equal q35b_quantize_nvfp4_bf16 applied, with the same scale, to the BF16
+ * output of q35b_gemm_w4a4_bf16 on the same weight.  w must be a gate/up weight with rows/2 a multiple of 64. */
+Q35B_API int q35b_gemm_w4a4_gate_up_nvfp4(const q35b_weight * w, const uint8_t * a_codes,
+                                          const uint8_t * a_scales_tiled, const float * input_scale_dev, int m,
+                                          uint8_t * out_codes, uint8_t * out_scales_tiled,
+                                          const float * out_scale_dev, unsigned int * status_dev, q35b_stream stream);
+
 /* Prefill projection for callers that cannot allocate device memory (no counterpart in the reference, whose
  * bridges all take caller-allocated scratch, include/qwen35x/runtime/cuda_bench.h:70-83).
  *

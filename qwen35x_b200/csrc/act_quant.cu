@@ -23,6 +23,7 @@
 
 #include "engine.h"
 #include "nvfp4_codec.cuh"
+#include "nvfp4_quant_block.cuh"
 
 namespace q35b {
 namespace {
@@ -117,36 +118,6 @@ __device__ __forceinline__ void load16<float>(const float * p, float (&v)[16]) {
     v[i * 4 + 2] = a.z;
     v[i * 4 + 3] = a.w;
   }
-}
-
-enum Recipe { kEngine = 0, kReference = 1 };
-
-// Quantise one 16-block; returns the scale byte, writes 8 code bytes.
-template <int RECIPE>
-__device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g, bool swap, uint2 & out) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  uint32_t sb;
-  float d;
-  if (RECIPE == kEngine) {
-    const float t = __fdiv_rn(amax, 6.0f);
-    sb = encode_ue4m3(fmaxf(__fdiv_rn(t, g), 1.0e-8f));
-    sb = sb > 0x7eu ? 0x7eu : sb;
-    d = __fmul_rn(fmaxf(decode_e4m3(static_cast<uint8_t>(sb)), 1.0e-8f), g);
-  } else {
-    d = fmaxf(__fdiv_rn(amax, 6.0f), 1.0e-8f);
-    sb = encode_ue4m3(d);
-  }
-  uint32_t word[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const uint32_t c = encode_e2m1(__fdiv_rn(v[i], d));
-    const int nib = swap ? (i ^ 1) : i;
-    word[nib >> 3] |= c << ((nib & 7) * 4);
-  }
-  out = make_uint2(word[0], word[1]);
-  return sb;
 }
 
 // Pass 2: one thread per 16-element block, so a warp reads 1 KB of contiguous activations and writes 256 bytes of

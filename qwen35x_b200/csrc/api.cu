@@ -340,6 +340,14 @@ int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes, const ui
                           status_dev, static_cast<cudaStream_t>(stream));
 }
 
+int q35b_gemm_w4a4_gate_up_nvfp4(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
+                                 const float * input_scale_dev, int m, uint8_t * out_codes, uint8_t * out_scales_tiled,
+                                 const float * out_scale_dev, unsigned int * status_dev, q35b_stream stream) {
+  const GemmQuantOut q{out_codes, out_scales_tiled, out_scale_dev};
+  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, nullptr, 0, nullptr, 0,
+                          status_dev, static_cast<cudaStream_t>(stream), &q);
+}
+
 int q35b_gemm_w4a4_bf16_residual(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
                                  const float * input_scale_dev, int m, const void * residual_bf16, int ldr, void * c_bf16,
                                  int ldc, unsigned int * status_dev, q35b_stream stream) {

@@ -84,9 +84,15 @@ size_t gemv_batch_bytes(const struct q35b_gemv_batch * b);
 
 // gemm_w4a4_tcgen05.cu
 int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, int box_rows);
+// Where a gate/up GEMM writes silu(gate) * up as an NVFP4 activation instead of BF16 (see gemm_epilogue.cuh).
+struct GemmQuantOut {
+  uint8_t * codes;          // [m, rows / 4] bytes
+  uint8_t * scales_tiled;   // tiled block scales of the [m, rows / 2] activation
+  const float * g_dev;      // its per-tensor scale, known in advance
+};
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
-                     cudaStream_t s);
+                     cudaStream_t s, const GemmQuantOut * qout = nullptr);
 
 
 // gemm_w4a4_2cta.cu

@@ -7,11 +7,19 @@
 //              silu(g) = g / (1 + exp(-g)): the SiLU-multiply the reference runs as a separate pass after its
 //              gate and up GEMMs (src/kernels/cuda/prefill.cu:674-678, pf_silu_mul_bf16), and half the bytes written.
 //   residual   replaces pf_add_residual_bf16 after the down / o projections (src/kernels/cuda/prefill.cu:679).
+//   gate/up -> NVFP4   the same SiLU-multiply, rounded to BF16 exactly as above, then quantised in place of being
+//              stored: the 16 outputs a thread holds per 32 accumulator columns are one NVFP4 block, so it writes
+//              8 code bytes and one scale byte of the tiled layout, ready to be the A operand of the down
+//              projection.  Replaces the reference's quantise pass between its gate/up and down GEMMs
+//              (src/runtime/cuda_bench.cu:2621-2660) and needs the activation's per-tensor scale in advance (the
+//              checkpoint's input_scale of the down projection, or a calibrated value).
 #pragma once
 
 #include <cuda_bf16.h>
 
 #include <cstdint>
+
+#include "nvfp4_quant_block.cuh"
 
 namespace q35b {
 
@@ -21,6 +29,12 @@ struct GemmEpilogue {
   int gate_up = 0;
   const __nv_bfloat16 * residual = nullptr;  // [m, n], row stride ldr
   int ldr = 0;
+  // gate/up -> NVFP4 (all three set, or none): codes [m, n/4] bytes, tiled scales of the [m, n/2] activation with
+  // q_slots = roundup(n/32, 4) scale columns per row, and that activation's per-tensor scale (device scalar)
+  uint8_t * q_codes = nullptr;
+  uint8_t * q_scales = nullptr;
+  const float * q_g = nullptr;
+  int q_slots = 0;
 };
 
 __device__ __forceinline__ void st_global_v8(void * p, const uint32_t (&v)[8]) {
@@ -41,6 +55,24 @@ __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int 
   const float alpha = g * ep.s2;
   if (ep.gate_up) {
     const float alpha_up = g * ep.s2_up;
+    if (ep.q_codes != nullptr) {
+      // n % 32 == 0 is checked on the host, so the chunk is whole
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float gv = __uint_as_float(r[16 * j + i]) * alpha;
+          const float uv = __uint_as_float(r[16 * j + 8 + i]) * alpha_up;
+          v[8 * j + i] = __bfloat162float(__float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv));
+        }
+      }
+      uint2 packed;
+      const uint32_t sb = quantize_block<kEngine>(v, __ldg(ep.q_g), false, packed);
+      *reinterpret_cast<uint2 *>(ep.q_codes + static_cast<size_t>(row) * (n >> 2) + (col0 >> 2)) = packed;
+      ep.q_scales[tiled_scale_offset(row, col0 >> 5, ep.q_slots)] = static_cast<uint8_t>(sb);
+      return;
+    }
     __nv_bfloat16 * dst = c + static_cast<size_t>(row) * ldc + (col0 >> 1);
     if (col0 + 32 <= n && ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0)) {
       uint32_t p[8];

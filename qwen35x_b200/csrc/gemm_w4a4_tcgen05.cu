@@ -404,12 +404,23 @@ int launch_tile(q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_s
 
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
-                     cudaStream_t s) {
-  if (w == nullptr || a_codes == nullptr || a_scales_tiled == nullptr || g_dev == nullptr || c_bf16 == nullptr) {
+                     cudaStream_t s, const GemmQuantOut * qout) {
+  if (w == nullptr || a_codes == nullptr || a_scales_tiled == nullptr || g_dev == nullptr ||
+      (c_bf16 == nullptr && qout == nullptr)) {
     return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection received a null device buffer.");
   }
   const int out_cols = w->gate_up ? w->rows / 2 : w->rows;
-  if (m <= 0 || ldc < out_cols) return fail(Q35B_ERR_SHAPE, "Invalid dimensions for NVFP4 prefill projection.");
+  if (m <= 0 || (qout == nullptr && ldc < out_cols)) return fail(Q35B_ERR_SHAPE, "Invalid dimensions for NVFP4 prefill projection.");
+  if (qout != nullptr) {
+    if (!w->gate_up) return fail(Q35B_ERR_ARGUMENT, "NVFP4 output of the prefill projection needs a gate/up weight.");
+    if (qout->codes == nullptr || qout->scales_tiled == nullptr || qout->g_dev == nullptr) {
+      return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection received a null device buffer.");
+    }
+    if ((out_cols % 64) != 0) return fail(Q35B_ERR_SHAPE, "NVFP4 output of the prefill projection needs rows / 2 to be a multiple of 64.");
+    if ((reinterpret_cast<uintptr_t>(qout->codes) & 7u) != 0) {
+      return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection buffers must be 16-byte aligned.");
+    }
+  }
   if (residual_bf16 != nullptr && (w->gate_up || ldr < w->rows)) {
     return fail(Q35B_ERR_ARGUMENT, "Invalid residual for NVFP4 prefill projection.");
   }
@@ -419,6 +430,12 @@ int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a
   ep.gate_up = w->gate_up ? 1 : 0;
   ep.residual = static_cast<const __nv_bfloat16 *>(residual_bf16);
   ep.ldr = ldr;
+  if (qout != nullptr) {
+    ep.q_codes = qout->codes;
+    ep.q_scales = qout->scales_tiled;
+    ep.q_g = qout->g_dev;
+    ep.q_slots = round_up_int(out_cols / 16, 4);
+  }
   if ((w->k % 64) != 0) return fail(Q35B_ERR_SHAPE, "NVFP4 W4A4 GEMM needs cols to be a multiple of 64.");
   if ((reinterpret_cast<uintptr_t>(a_codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a_scales_tiled) & 15u) != 0) {
     return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection buffers must be 16-byte aligned.");

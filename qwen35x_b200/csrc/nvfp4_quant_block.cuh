@@ -1,0 +1,47 @@
+// One 16-element NVFP4 block: amax -> UE4M3 scale byte -> sixteen E2M1 codes.  Shared by the stand-alone
+// quantiser (act_quant.cu) and the GEMM epilogue that emits quantised activations (gemm_epilogue.cuh), so that
+// both produce the same bits from the same values.
+//
+// Recipes (all fp32, IEEE division, no fused contraction that could change a rounding):
+//   engine     t = amax_blk / 6; sb = min(UE4M3(max(t / g, 1e-8)), 0x7e); d = max(decode(sb), 1e-8) * g
+//   reference  d = max(amax_blk / 6, 1e-8); sb = UE4M3(d)      (src/runtime/cuda_bench.cu:98-213)
+//   code_i = E2M1(x_i / d), element 2j in the low nibble (or swapped for the reference's cuBLASLt order)
+#pragma once
+
+#include <cstdint>
+
+#include "nvfp4_codec.cuh"
+
+namespace q35b {
+
+enum Recipe { kEngine = 0, kReference = 1 };
+
+// Quantise one 16-block; returns the scale byte, writes 8 code bytes.
+template <int RECIPE>
+__device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g, bool swap, uint2 & out) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  uint32_t sb;
+  float d;
+  if (RECIPE == kEngine) {
+    const float t = __fdiv_rn(amax, 6.0f);
+    sb = encode_ue4m3(fmaxf(__fdiv_rn(t, g), 1.0e-8f));
+    sb = sb > 0x7eu ? 0x7eu : sb;
+    d = __fmul_rn(fmaxf(decode_e4m3(static_cast<uint8_t>(sb)), 1.0e-8f), g);
+  } else {
+    d = fmaxf(__fdiv_rn(amax, 6.0f), 1.0e-8f);
+    sb = encode_ue4m3(d);
+  }
+  uint32_t word[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t c = encode_e2m1(__fdiv_rn(v[i], d));
+    const int nib = swap ? (i ^ 1) : i;
+    word[nib >> 3] |= c << ((nib & 7) * 4);
+  }
+  out = make_uint2(word[0], word[1]);
+  return sb;
+}
+
+}  // namespace q35b

@@ -86,6 +86,8 @@ def lib() -> C.CDLL:
     L.q35b_project_prefill_bf16_static.argtypes = [vp, vp, i, f, vp, i, vp]
     L.q35b_gemm_w4a4_bf16_residual.restype = i
     L.q35b_gemm_w4a4_bf16_residual.argtypes = [vp, vp, vp, vp, i, vp, i, vp, i, vp, vp]
+    L.q35b_gemm_w4a4_gate_up_nvfp4.restype = i
+    L.q35b_gemm_w4a4_gate_up_nvfp4.argtypes = [vp, vp, vp, vp, i, vp, vp, vp, vp, vp]
     L.q35b_debug_encode_ue4m3.restype = C.c_uint8
     L.q35b_debug_encode_ue4m3.argtypes = [f]
     L.q35b_debug_encode_e2m1.restype = C.c_uint8
@@ -356,6 +358,21 @@ def gemm_w4a4(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, out=None,
                                                   g.data_ptr(), m, residual.data_ptr(), residual.stride(0),
                                                   out.data_ptr(), out.stride(0), st, _stream_ptr(torch)))
     return out
+
+
+def gemm_w4a4_gate_up_quant(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, out_scale, scratch=None, status=None):
+    """Gate/up prefill projection whose epilogue quantises silu(gate) * up to NVFP4 with the given per-tensor scale
+    (`out_scale`: 1-element fp32 device tensor) -> (codes [m, rows/4] uint8, tiled scales, out_scale), the A operand
+    of the down projection's gemm_w4a4.  `scratch` = act_scratch(m, rows // 2, device) to reuse buffers."""
+    torch = _torch()
+    assert weight.gate_up and out_scale.dtype == torch.float32 and out_scale.is_cuda
+    inter = weight.rows // 2
+    codes, scales, _ = scratch if scratch is not None else act_scratch(m, inter, a_codes.device)
+    st = status.data_ptr() if status is not None else None
+    _check(lib().q35b_gemm_w4a4_gate_up_nvfp4(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(), g.data_ptr(), m,
+                                              codes.data_ptr(), scales.data_ptr(), out_scale.data_ptr(), st,
+                                              _stream_ptr(torch)))
+    return codes.view(m, inter // 2), scales, out_scale
 
 
 def project_prefill(weight: Nvfp4Weight, x, out=None, scratch=None, global_scale: float = 0.0, residual=None):

@@ -148,3 +148,67 @@ def test_prefill_gate_up_silu(engine, oracle, m, n_half):
         _, up = oracle.gemm_w4a4(u_codes[r:r + 1], u_scales[r:r + 1], u_s2, e_codes, e_scales, e_g, threads=8)
         exp[:, j] = (gate / (1 + np.exp(-gate)) * up)[:, 0]
     assert oracle.rel_l2(got, oracle.bf16_to_f32(oracle.bf16_round(exp))) <= REL_L2_TOL
+
+
+def _untile(oracle, tiled: np.ndarray, rows: int, scale_cols: int) -> np.ndarray:
+    """Row-major [rows, scale_cols] view of a tiled scale array (padding dropped)."""
+    out = np.zeros((rows, scale_cols), dtype=np.uint8)
+    for r in range(rows):
+        for c in range(scale_cols):
+            out[r, c] = tiled[oracle.tiled_scale_offset(r, c, scale_cols)]
+    return out
+
+
+@pytest.mark.parametrize("m,n_half,shrink", [(300, 384, 1.0), (100, 384, 1.0), (257, 192, 8.0), (64, 64, 1.0)])
+def test_prefill_gate_up_to_nvfp4(engine, oracle, m, n_half, shrink):
+    """The gate/up GEMM that writes silu(gate) * up as an NVFP4 activation: its codes and block scales equal the
+    stand-alone quantiser applied, with the same per-tensor scale, to the BF16 output of the plain gate/up GEMM
+    (bit for bit, also when the scale is too small and values saturate), and the down projection on that activation
+    meets the oracle within relative L2 <= 1e-3."""
+    import torch
+
+    k = 512
+    _, g_codes, g_scales, g_s2 = make_weight(n_half, k, seed=61, std=0.05)
+    _, u_codes, u_scales, u_s2 = make_weight(n_half, k, seed=62, std=0.03)
+    xb = make_activations(m, k, seed=63, outlier_frac=0.001)
+    w = engine.Nvfp4Weight.gate_up_from_host(g_codes, g_scales, g_s2, u_codes, u_scales, u_s2)
+    a_codes, a_scales, g = engine.quantize_activations(to_torch_bf16(xb))
+    c = engine.gemm_w4a4(w, a_codes, a_scales, g, m)
+    scale = float(c.float().abs().max().item()) / (6.0 * 448.0) / shrink
+    out_scale = torch.tensor([scale], dtype=torch.float32, device="cuda")
+    scale = float(out_scale.item())  # the fp32 value both paths see
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    f_codes, f_scales, _ = engine.gemm_w4a4_gate_up_quant(w, a_codes, a_scales, g, m, out_scale, status=status)
+    u_codes_q, u_scales_q, u_g = engine.quantize_activations(c, global_scale=scale)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and float(u_g.item()) == scale
+    assert torch.equal(f_codes.reshape(-1), u_codes_q.reshape(-1)[: m * n_half // 2])
+    f_rm = _untile(oracle, f_scales.cpu().numpy(), m, n_half // 16)
+    assert np.array_equal(f_rm, _untile(oracle, u_scales_q.cpu().numpy(), m, n_half // 16))
+    # and against the oracle's quantiser on the same BF16 values
+    e_codes, e_scales, _ = oracle.quantize_nvfp4(from_torch_bf16(c), global_scale=scale)
+    assert np.array_equal(f_codes.cpu().numpy().reshape(m, n_half // 2), e_codes) and np.array_equal(f_rm, e_scales)
+    # down projection fed by the fused output
+    n_out = 256
+    _, d_codes, d_scales, d_s2 = make_weight(n_out, n_half, seed=64)
+    wd = engine.Nvfp4Weight.from_host(d_codes, d_scales, d_s2)
+    y = engine.gemm_w4a4(wd, f_codes, f_scales, out_scale, m, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    eb, _ = oracle.gemm_w4a4(d_codes, d_scales, d_s2, e_codes, e_scales, scale, threads=8)
+    assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(y)), oracle.bf16_to_f32(eb)) <= REL_L2_TOL
+
+
+def test_prefill_gate_up_to_nvfp4_rejects(engine):
+    import torch
+
+    _, codes, scales, s2 = make_weight(256, 256, seed=1)
+    plain = engine.Nvfp4Weight.from_host(codes, scales, s2)
+    a_codes, a_scales, g = engine.quantize_activations(torch.zeros((8, 256), dtype=torch.bfloat16, device="cuda"))
+    one = torch.ones(1, dtype=torch.float32, device="cuda")
+    with pytest.raises(AssertionError):
+        engine.gemm_w4a4_gate_up_quant(plain, a_codes, a_scales, g, 8, one)
+    odd = engine.Nvfp4Weight.gate_up_from_host(codes[:48], scales[:48], s2, codes[48:96], scales[48:96], s2)
+    with pytest.raises(engine.Q35bError) as e:
+        engine.gemm_w4a4_gate_up_quant(odd, a_codes, a_scales, g, 8, one)
+    assert e.value.status == 2
