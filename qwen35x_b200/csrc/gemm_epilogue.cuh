@@ -43,6 +43,9 @@ __device__ __forceinline__ void st_global_v8(void * p, const uint32_t (&v)[8]) {
                : "memory");
 }
 
+// silu(g) * u with the hardware exponential and reciprocal (a few fp32 ulp, far inside the BF16 rounding that follows)
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t *>(&h);
@@ -64,7 +67,7 @@ __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int 
         for (int i = 0; i < 8; ++i) {
           const float gv = __uint_as_float(r[16 * j + i]) * alpha;
           const float uv = __uint_as_float(r[16 * j + 8 + i]) * alpha_up;
-          v[8 * j + i] = __bfloat162float(__float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv));
+          v[8 * j + i] = __bfloat162float(__float2bfloat16_rn(silu_mul(gv, uv)));
         }
       }
       uint2 packed;
@@ -82,7 +85,7 @@ __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int 
         for (int i = 0; i < 8; i += 2) {
           const float g0 = __uint_as_float(r[16 * j + i]) * alpha, g1 = __uint_as_float(r[16 * j + i + 1]) * alpha;
           const float u0 = __uint_as_float(r[16 * j + 8 + i]) * alpha_up, u1 = __uint_as_float(r[16 * j + 8 + i + 1]) * alpha_up;
-          p[4 * j + (i >> 1)] = pack_bf16(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+          p[4 * j + (i >> 1)] = pack_bf16(silu_mul(g0, u0), silu_mul(g1, u1));
         }
       }
       st_global_v8(dst, p);
@@ -92,7 +95,7 @@ __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int 
           if (col0 + 16 * j + 8 + i < n) {
             const float gv = __uint_as_float(r[16 * j + i]) * alpha;
             const float uv = __uint_as_float(r[16 * j + 8 + i]) * alpha_up;
-            dst[8 * j + i] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+            dst[8 * j + i] = __float2bfloat16_rn(silu_mul(gv, uv));
           }
         }
       }

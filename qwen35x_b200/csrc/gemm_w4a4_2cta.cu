@@ -44,8 +44,14 @@ constexpr int kSfaBytes = kMmaPerStage * kSfChunk;
 constexpr int kSfbBytes = 2 * kMmaPerStage * kSfChunk;
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 34816
 constexpr int kStages = 6;
-constexpr int kThreads = 192;
+#ifndef Q35B_EPI_WARPS
+#define Q35B_EPI_WARPS 12
+#endif
+constexpr int kEpilogueWarps = Q35B_EPI_WARPS;  // kEpilogueWarps / 4 per TMEM lane quarter, each a column slice
+constexpr int kThreads = (2 + kEpilogueWarps) * 32;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kEpiCols = kTileN / (kEpilogueWarps / 4);  // columns drained by one epilogue warp
+static_assert(kEpilogueWarps % 4 == 0 && kEpiCols % 32 == 0 && kEpiCols * (kEpilogueWarps / 4) == kTileN, "epilogue column split");
 constexpr int kAccCols = 2 * kTileN;     // two accumulators
 constexpr int kSfaCols = kMmaPerStage * 4;
 constexpr int kSfbCols = kMmaPerStage * 8;
@@ -68,6 +74,9 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) 
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(bar), "r"(cta));
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
@@ -173,8 +182,9 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint64_t * full = bars;                       // used in the leader: bytes of both CTAs
   uint64_t * empty = bars + kStages;            // in each CTA: its own stages are free
   uint64_t * tmem_full = bars + 2 * kStages;    // [2] in each CTA: accumulator b is complete
-  uint64_t * tmem_empty = tmem_full + 2;        // [2] used in the leader: both CTAs have drained accumulator b
-  uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+  uint64_t * drained = tmem_full + 2;           // [2] in each CTA: its epilogue warps have read accumulator b out of TMEM
+  uint64_t * peer_drained = drained + 2;        // [2] used in the leader: the partner CTA has drained accumulator b
+  uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(peer_drained + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -192,7 +202,8 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(tmem_full + i), 1);
-      mbar_init(smem_u32(tmem_empty + i), 8);  // four epilogue warps in each of the two CTAs
+      mbar_init(smem_u32(drained + i), kEpilogueWarps);
+      mbar_init(smem_u32(peer_drained + i), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -259,7 +270,8 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
         const uint32_t ab = li & 1;
-        if (!mbar_wait(smem_u32(tmem_empty + ab), ((li >> 1) & 1) ^ 1)) {
+        if (!mbar_wait(smem_u32(drained + ab), ((li >> 1) & 1) ^ 1) ||
+            !mbar_wait(smem_u32(peer_drained + ab), ((li >> 1) & 1) ^ 1)) {
           atomicExch(status, kMmaDrainWait);
           ok = false;
           break;
@@ -303,10 +315,23 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         if (ok) umma_commit_pair(smem_u32(tmem_full + ab));
       }
+    } else if (rank == 1 && elect_one() && !aborted) {
+      // ---------------- drain forwarder (partner CTA): tells the leader when this CTA's epilogue warps have
+      // read an accumulator out, so that none of them spends a cluster round trip on it ----------------
+      uint32_t li = 0;
+      for (int tile = pair; tile < num_tiles; tile += num_pairs, ++li) {
+        const uint32_t ab = li & 1;
+        if (!mbar_wait(smem_u32(drained + ab), (li >> 1) & 1)) {
+          atomicExch(status, kEpilogueWait);
+          break;
+        }
+        mbar_arrive_cluster(smem_u32(peer_drained + ab), 0);
+      }
     }
   } else {
     // ---------------- epilogue (both CTAs): this CTA's 128 rows of the pair's tile ----------------
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;                 // TMEM lanes 32 * quarter .. + 31 (fixed by the warp's index)
+    const int col_base = ((warp - 2) >> 2) * kEpiCols;
     const float g = __ldg(g_dev);
     uint32_t li = 0;
     bool ok = !aborted;
@@ -321,19 +346,18 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = tm * kTileM + static_cast<int>(rank) * kCtaRows + quarter * 32 + lane;
-      const uint32_t taddr = tmem_acc + ab * kTileN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < kTileN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 32 == kTileN) {
-          // last TMEM read of this tile: hand the accumulator back before the stores go out
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(smem_u32(tmem_empty + ab), 0);
-        }
-        if (row < m) gemm_store_chunk32(r, row, tn * kTileN + c0, n, g, ep, c, ldc);
+      const uint32_t taddr = tmem_acc + ab * kTileN + col_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      // read the warp's whole share into registers, give the accumulator back at once, then convert and store
+      uint32_t r[kEpiCols / 32][32];
+#pragma unroll
+      for (int j = 0; j < kEpiCols / 32; ++j) tmem_ld32(taddr + 32 * j, r[j]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(drained + ab));
+      if (row < m) {
+#pragma unroll
+        for (int j = 0; j < kEpiCols / 32; ++j) gemm_store_chunk32(r[j], row, tn * kTileN + col_base + 32 * j, n, g, ep, c, ldc);
       }
     }
   }

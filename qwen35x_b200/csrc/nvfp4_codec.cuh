@@ -110,15 +110,19 @@ Q35B_HD uint8_t encode_e2m1_scan(float value) {
 
 // fp32 -> E2M1 nibble, nearest magnitude with ties to the smaller one, sign
 // bit = (value < 0) (src/runtime/cuda_bench.cu:926-940).
-Q35B_HD uint8_t encode_e2m1(float value) {
-  const uint32_t u = f32_bits(value);
-  const uint32_t au = u & 0x7fffffffu;
-  if (au >= 0x49800000u) {  // |v| >= 2^20, inf or NaN: rare, follow the scan
-    return encode_e2m1_scan(value);
-  }
-  const float a = bits_f32(au);
+// The same for |value| < 2^20 or NaN (the scan also gives 0 for NaN): no range check, no branch.
+Q35B_HD uint8_t encode_e2m1_bounded(float value) {
+  const float a = bits_f32(f32_bits(value) & 0x7fffffffu);
   const unsigned code = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
   return static_cast<uint8_t>(((value < 0.0f) ? 8u : 0u) | code);
+}
+
+Q35B_HD uint8_t encode_e2m1(float value) {
+  const uint32_t au = f32_bits(value) & 0x7fffffffu;
+  if (au >= 0x49800000u && au <= 0x7f800000u) {  // 2^20 <= |v| <= inf: rare, follow the scan
+    return encode_e2m1_scan(value);
+  }
+  return encode_e2m1_bounded(value);
 }
 
 // Round-to-nearest-even fp32 -> bf16 bits (NaN kept quiet), the reference's

@@ -16,6 +16,20 @@ namespace q35b {
 
 enum Recipe { kEngine = 0, kReference = 1 };
 
+// x / d rounded to nearest, for a divisor whose refined reciprocal r is at hand: quotient estimate, then two
+// residual corrections, the last one delivering the rounded result.  The block's sixteen quotients share one
+// divisor, so this replaces sixteen full divisions (each with its own reciprocal and range check) by one
+// reciprocal and five dependent-free FMA-pipe instructions per element.  Used only when the block's divisor and
+// amax are far from the exponent limits (see quantize_block); tests/test_quant_gpu.py feeds it values placed
+// ulp by ulp around every rounding boundary of the E2M1 encoder and compares with IEEE division on the host.
+__device__ __forceinline__ float div_by_shared(float x, float d, float r) {
+  float q = __fmul_rn(x, r);
+  float e = __fmaf_rn(-d, q, x);
+  q = __fmaf_rn(e, r, q);
+  e = __fmaf_rn(-d, q, x);
+  return __fmaf_rn(e, r, q);
+}
+
 // Quantise one 16-block; returns the scale byte, writes 8 code bytes.
 template <int RECIPE>
 __device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g, bool swap, uint2 & out) {
@@ -34,11 +48,27 @@ __device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g
     sb = encode_ue4m3(d);
   }
   uint32_t word[2] = {0u, 0u};
+  // exponents of d and amax inside [2^-60, 2^60]: no intermediate of div_by_shared can overflow, and a quotient
+  // small enough to lose bits is far below the first rounding boundary (0.25); amax < 2^19 d keeps every quotient
+  // inside the range of the branch-free encoder
+  const uint32_t de = (__float_as_uint(d) >> 23) & 0xffu, ae = (__float_as_uint(amax) >> 23) & 0xffu;
+  if (de >= 67u && de <= 187u && ae <= 187u && amax < d * 524288.0f) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    r = __fmaf_rn(r, __fmaf_rn(-d, r, 1.0f), r);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const uint32_t c = encode_e2m1(__fdiv_rn(v[i], d));
-    const int nib = swap ? (i ^ 1) : i;
-    word[nib >> 3] |= c << ((nib & 7) * 4);
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t c = encode_e2m1_bounded(div_by_shared(v[i], d, r));
+      const int nib = swap ? (i ^ 1) : i;
+      word[nib >> 3] |= c << ((nib & 7) * 4);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t c = encode_e2m1(__fdiv_rn(v[i], d));
+      const int nib = swap ? (i ^ 1) : i;
+      word[nib >> 3] |= c << ((nib & 7) * 4);
+    }
   }
   out = make_uint2(word[0], word[1]);
   return sb;

@@ -2,7 +2,7 @@
 
 Covers the named shapes of the benchmark configurations: the single 0.8B gate_proj projection, the 0.8B and 4B-class
 decode steps at M = 1, 2, 4, 8 (work-list launch), the 4B-class prefill GEMMs at M = 512 and 4096 (GEMM alone and
-activation quantisation + GEMM), and the (K, N) x M sweep with 1 % of weight rows scaled x8.  Every entry gives
+activation quantisation + GEMM), the 4B-class prefill MLP block with and without the NVFP4-writing gate/up epilogue, and the (K, N) x M sweep with 1 % of weight rows scaled x8.  Every entry gives
 microseconds, GB/s of algorithmic bytes (decode) or TFLOP/s (prefill), and the fraction of the HBM or FP4-tensor
 roofline.  Inputs are seeded synthetic tensors quantised on the GPU; weights are rotated through enough copies that
 no launch finds its operands in L2.
@@ -178,11 +178,66 @@ def gemm_entries(q, torch, device, peaks, n, k, ms, label, row_outliers=False):
     return out
 
 
+def mlp_entries(q, torch, device, peaks, hidden, inter, ms, label):
+    """Prefill MLP block x -> down(silu(gate x) * up x) + residual: the chain with the gate/up GEMM writing BF16 and a
+    separate quantise pass before the down projection, and the chain whose gate/up epilogue writes NVFP4 directly."""
+    out = []
+    gen = torch.Generator(device=device).manual_seed(31)
+    stream = torch.cuda.Stream(device=device)
+    for m in ms:
+        per_set = (3 * hidden * inter) * 9 // 16 + m * inter * 2 + 3 * m * hidden * 2
+        sets = max(2, min(6, -(-int(1.3 * L2_BYTES) // per_set)))
+        data = []
+        for _ in range(sets):
+            g_c, g_s, g_s2 = _make_weight(q, torch, device, gen, inter, hidden)
+            u_c, u_s, u_s2 = _make_weight(q, torch, device, gen, inter, hidden)
+            gu = q.Nvfp4Weight.gate_up_from_host(g_c.cpu().numpy(), g_s.cpu().numpy(), float(g_s2), u_c.cpu().numpy(),
+                                                 u_s.cpu().numpy(), float(u_s2))
+            d_c, d_s, d_s2 = _make_weight(q, torch, device, gen, hidden, inter)
+            down = q.Nvfp4Weight.from_device(d_c, d_s, d_s2)
+            del g_c, g_s, u_c, u_s, d_c, d_s
+            x = torch.randn((m, hidden), generator=gen, device=device).to(torch.bfloat16)
+            res = torch.randn((m, hidden), generator=gen, device=device).to(torch.bfloat16)
+            sx = q.act_scratch(m, hidden, device)
+            sh = q.act_scratch(m, inter, device)
+            h = torch.empty((m, inter), dtype=torch.bfloat16, device=device)
+            y = torch.empty((m, hidden), dtype=torch.bfloat16, device=device)
+            # calibrate the intermediate activation's scale once
+            q.project_prefill(gu, x, out=h, scratch=sx)
+            h_scale = (h.float().abs().max() / (6.0 * 448.0)).reshape(1).to(torch.float32)
+            data.append((gu, down, x, res, sx, sh, h, y, h_scale))
+        torch.cuda.synchronize()
+
+        def two_pass(d):
+            gu, down, x, res, sx, sh, h, y, h_scale = d
+            q.project_prefill(gu, x, out=h, scratch=sx)
+            q.project_prefill(down, h, out=y, scratch=sh, residual=res)
+
+        def fused(d):
+            gu, down, x, res, sx, sh, h, y, h_scale = d
+            codes, scales, g = q.quantize_activations(x, scratch=sx)
+            hc, hs, hg = q.gemm_w4a4_gate_up_quant(gu, codes, scales, g, m, h_scale, scratch=sh)
+            q.gemm_w4a4(down, hc, hs, hg, m, out=y, residual=res)
+
+        flops = 2.0 * m * hidden * inter * 3
+        row = {"workload": label, "M": m, "hidden": hidden, "intermediate": inter, "GFLOP": round(flops / 1e9, 1),
+               "l2": f"{sets} weight/activation sets rotated"}
+        for name, fn in (("bf16_intermediate_then_quantise", two_pass), ("nvfp4_intermediate_from_epilogue", fused)):
+            graphs = [_capture(torch, stream, lambda d=d: fn(d)) for d in data]
+            us = _time_graphs(torch, stream, graphs, reps=sets * 2)
+            row[name] = {"us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1)}
+        out.append(row)
+        del data
+        torch.cuda.empty_cache()
+    return out
+
+
 def run(path: str, q, torch, device, peaks) -> dict:
     shapes_0p8b = [(4096, 1024), (1024, 2048), (7168, 1024), (1024, 3584)]
     shapes_4b = [(18432, 2560), (2560, 9216), (10240, 2560), (2560, 4096)]
     sweep = [(3584, 1024), (9216, 2560), (2560, 9216), (32768, 2560)]  # (N, K)
-    report = {"peaks": peaks, "decode": [], "single_projection": [], "prefill": [], "sweep_decode": [], "sweep_prefill": []}
+    report = {"peaks": peaks, "decode": [], "single_projection": [], "prefill": [], "prefill_mlp": [], "sweep_decode": [],
+              "sweep_prefill": []}
     report["single_projection"] += single_projection_entries(q, torch, device, peaks, 3584, 1024, [1],
                                                              "config 1: 0.8B gate_proj, single projection")
     report["decode"] += decode_entries(q, torch, device, peaks, shapes_0p8b, 24, [1, 2, 4, 8], "config 2: 0.8B-class decode step")
@@ -190,6 +245,7 @@ def run(path: str, q, torch, device, peaks) -> dict:
     torch.cuda.empty_cache()
     for n, k in ((18432, 2560), (2560, 9216)):
         report["prefill"] += gemm_entries(q, torch, device, peaks, n, k, [512, 4096], "config 4: 4B-class prefill")
+    report["prefill_mlp"] += mlp_entries(q, torch, device, peaks, 2560, 9216, [512, 4096], "4B-class prefill MLP block")
     for n, k in sweep:
         report["sweep_decode"] += single_projection_entries(q, torch, device, peaks, n, k, [1], "config 5 sweep (1% rows x8)",
                                                             row_outliers=True)

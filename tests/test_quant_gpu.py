@@ -115,3 +115,35 @@ def test_full_size_round_trip_property(engine, oracle):
     same = (codes2 == codes).float().mean().item()
     # not exactly idempotent: rounding the dequantised values to BF16 moves some across a code boundary
     assert same > 0.9
+
+
+def test_division_at_every_rounding_boundary(engine, oracle):
+    """The block quantiser divides sixteen values by one shared divisor with a reciprocal-and-correct sequence
+    instead of sixteen IEEE divisions.  Values are placed -3..+3 ulp around d times every E2M1 rounding boundary
+    (0.25 .. 5.0), for thousands of divisors d spread over 60 binary orders of magnitude (so that both the
+    shared-reciprocal path and the plain-division path for extreme exponents run): codes must equal the oracle's,
+    which divides with the host's IEEE division."""
+    import torch
+
+    rng = np.random.default_rng(77)
+    e4 = oracle.decode_e4m3_table().astype(np.float32)
+    bounds = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    n, k = 64, 1024
+    for trial in range(12):
+        top = np.float32(10.0 ** rng.uniform(-25, 25))
+        w = np.zeros((n, k), dtype=np.float32)
+        amax = (top * 10.0 ** rng.uniform(-6, 0, size=(n, k // 16))).astype(np.float32)
+        amax[0, 0] = top
+        w[:, 0::16] = amax * rng.choice(np.array([-1.0, 1.0], dtype=np.float32), size=amax.shape)
+        _, scales0, g = oracle.quantize_nvfp4(w)
+        d = (np.maximum(e4[scales0], np.float32(1e-8)) * np.float32(g)).astype(np.float32)  # [n, k/16]
+        for j in range(1, 16):
+            target = (bounds[rng.integers(0, 7, size=d.shape)] * d).astype(np.float32)
+            bits = target.view(np.int32) + rng.integers(-3, 4, size=d.shape, dtype=np.int32)
+            w[:, j::16] = bits.view(np.float32) * rng.choice(np.array([-1.0, 1.0], dtype=np.float32), size=d.shape)
+        e_codes, e_scales, e_g = oracle.quantize_nvfp4(w)
+        assert np.array_equal(e_scales, scales0) and e_g == g  # the probes did not move any amax
+        codes, scales, s2 = engine.quantize_weight(torch.from_numpy(w).cuda())
+        assert np.float32(s2).view(np.uint32) == np.float32(e_g).view(np.uint32)
+        assert np.array_equal(scales.cpu().numpy(), e_scales)
+        assert np.array_equal(codes.cpu().numpy(), e_codes), f"trial {trial}: {(codes.cpu().numpy() != e_codes).sum()} code bytes differ"
