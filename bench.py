@@ -40,8 +40,8 @@ GEMM_M = 4096
 GEMM_SETS = 5
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes of one launch from the ncu captures summarised under profiles/ (same workloads as below)
-DECODE_DRAM_TRAFFIC_BYTES = 234_193_152 + 5_075_200
-GEMM_DRAM_TRAFFIC_BYTES = 32_959_488 + 98_072_832
+DECODE_DRAM_TRAFFIC_BYTES = 234_200_320 + 5_327_616
+GEMM_DRAM_TRAFFIC_BYTES = 32_540_672 + 100_419_584
 
 
 def algorithmic_bytes(n: int, k: int, m: int) -> int:
@@ -525,6 +525,7 @@ def main() -> int:
         rep["cpu_reference"] = cpu_reference_entries([(3584, 1024, 1), (18432, 2560, 1), (2560, 9216, 1), (18432, 2560, 4096)])
         Path(args.report).parent.mkdir(parents=True, exist_ok=True)
         Path(args.report).write_text(json.dumps(rep, indent=1))
+        Path(args.report).with_suffix(".md").write_text(shape_report.to_markdown(rep))
         print(json.dumps({"report": args.report, "entries": sum(len(v) for v in rep.values() if isinstance(v, list))}))
         return 0
     if args.impl == "reference":

@@ -255,3 +255,60 @@ def run(path: str, q, torch, device, peaks) -> dict:
         with open(path, "w") as f:
             json.dump(report, f, indent=1)
     return report
+
+
+def to_markdown(report: dict) -> str:
+    """The report as the tables kept under profiles/ (written next to the JSON by `bench.py --report`)."""
+    pk = report["peaks"]
+    out = ["# Per-shape throughput report (1 x B200)", "",
+           "Command: `python bench.py --report <path>.json` (CUDA-graph replays, CUDA events on the launching stream, "
+           "median of 5 blocks; weights/operands rotated through more than L2-size worth of copies; synthetic seeded "
+           f"tensors quantised on the GPU). Peaks: measured HBM copy {pk['hbm_gbs']:.0f} GB/s; FP4 tensor: nominal "
+           f"{FP4_NOMINAL_TFLOPS:.0f} TFLOP/s dense (no measured FP4 peak exists; 4 x measured BF16 burst = "
+           f"{4 * pk['bf16_tflops']:.0f} TFLOP/s is shown beside it).", ""]
+
+    def decode_table(title, rows, shape_cols):
+        out.extend([f"## {title}", ""])
+        head = ["workload", "M"] + (["N", "K"] if shape_cols else ["projections"]) + ["MB", "us", "GB/s", "of HBM peak", "kernel"]
+        out.append("| " + " | ".join(head) + " |")
+        out.append("|" + "---|" * len(head))
+        for r in rows:
+            mid = [str(r["N"]), str(r["K"])] if shape_cols else [str(r["projections"])]
+            out.append("| " + " | ".join([r["workload"], str(r["M"])] + mid + [f"{r['bytes'] / 1e6:.1f}", f"{r['us']:.2f}",
+                                          f"{r['GB/s']:.1f}", f"{r['hbm_frac']:.3f}", "`" + r["kernel"].split(" ")[0] + "`"]) + " |")
+        out.append("")
+
+    def gemm_table(title, rows):
+        out.extend([f"## {title}", ""])
+        head = ["workload", "M", "N", "K", "GFLOP", "GEMM us", "TFLOP/s", "of 9 PF nominal", "of 4xBF16 measured",
+                "quantise+GEMM us", "kernel"]
+        out.append("| " + " | ".join(head) + " |")
+        out.append("|" + "---|" * len(head))
+        for r in rows:
+            g, qg = r["gemm_only"], r["quant_gemm"]
+            out.append("| " + " | ".join([r["workload"], str(r["M"]), str(r["N"]), str(r["K"]), str(r["GFLOP"]), f"{g['us']:.2f}",
+                                          f"{g['TFLOP/s']:.1f}", f"{g['fp4_nominal_frac']:.3f}", f"{g['frac_of_4x_measured_bf16']:.3f}",
+                                          f"{qg['us']:.2f}", "`" + r["kernel"] + "`"]) + " |")
+        out.append("")
+
+    decode_table("Decode (W4A16, one work-list launch over all projections of a step)", report["decode"], False)
+    decode_table("Single projection per launch (decode)", report["single_projection"] + report["sweep_decode"], True)
+    gemm_table("Prefill (W4A4 tcgen05 GEMM)", report["prefill"] + report["sweep_prefill"])
+    if report.get("prefill_mlp"):
+        out.extend(["## Prefill MLP block: down(silu(gate x) * up x) + residual", "",
+                    "| workload | M | hidden | intermediate | GFLOP | BF16 intermediate + quantise pass us | TFLOP/s | "
+                    "NVFP4 intermediate from the gate/up epilogue us | TFLOP/s |", "|" + "---|" * 9])
+        for r in report["prefill_mlp"]:
+            a, b = r["bf16_intermediate_then_quantise"], r["nvfp4_intermediate_from_epilogue"]
+            out.append(f"| {r['workload']} | {r['M']} | {r['hidden']} | {r['intermediate']} | {r['GFLOP']} | {a['us']:.2f} | "
+                       f"{a['TFLOP/s']:.1f} | {b['us']:.2f} | {b['TFLOP/s']:.1f} |")
+        out.append("")
+    if report.get("cpu_reference"):
+        out.extend(["## Reference CPU path (oracle port of the scalar loop), same box", "",
+                    "| shape (N, K, M) | 1 thread us (extrapolated) | all threads us (extrapolated) | cores | sample |",
+                    "|---|---:|---:|---:|---|"])
+        for r in report["cpu_reference"]:
+            allk = [k for k in r if k.startswith("cpu_us_") and not k.startswith("cpu_us_1_")][0]
+            out.append(f"| ({r['N']}, {r['K']}, {r['M']}) | {r['cpu_us_1_thread_extrapolated']:.0f} | {r[allk]:.0f} | {r['cores']} | {r['sample']} |")
+        out.append("")
+    return "\n".join(out)
