@@ -325,15 +325,20 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
         raise
     widest = max(c for _, c in sharding.shard_layout(n, world))
     gathered = torch.empty((world * m, widest), dtype=torch.bfloat16, device=device) if world > 1 else None
+    # the gather fused into the GEMM's stores: every rank owns a full [m, n] matrix the other ranks store into
+    peer = sharding.PeerGather(m, n) if world > 1 else None
     counter = [0]
 
-    def one(with_quant: bool, with_gather: bool, index=None):
+    def one(with_quant: bool, with_gather: bool, index=None, fused: bool = True):
         weight, x, scratch, out = sets[(counter[0] if index is None else index) % GEMM_SETS]
         counter[0] += 1
         if with_quant:
             a_codes, a_scales, g = q.quantize_activations(x, scratch=scratch)
         else:
             a_codes, a_scales, g = scratch[0].view(m, k // 2), scratch[1], scratch[2]
+        if world > 1 and with_gather and fused:
+            peer.project(weight, a_codes, a_scales, g)  # GEMM storing into every rank's [m, n] + bounded wait
+            return
         q.gemm_w4a4(weight, a_codes, a_scales, g, m, out=out)
         if world > 1 and with_gather:
             sharding.all_gather_slabs(out, n, out=gathered)  # result layout [rank][M][rows of rank]
@@ -378,6 +383,9 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
             graphs[gi[0] % GEMM_SETS].replay()
             gi[0] += 1
     ms_full = timed(full_step, steps, max(3, args.warmup))
+    ms_nccl = timed(lambda: one(True, True, fused=False), steps, max(3, args.warmup)) if world > 1 else None
+    if peer is not None:
+        peer.check()
     flops = 2.0 * m * n * k
     fp4_peak_nominal = 9000.0
     fp4_peak_4x = 4.0 * pk["bf16_tflops"]
@@ -385,7 +393,11 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
     return {
         "workload": f"prefill W4A4 GEMM M={m}, gate+up [N={n}, K={k}] (BASELINE configs[3]), N-sharded over {world} GPU(s)",
         "gemm_only": {"ms": round(ms_gemm, 4), "tflops": round(tf, 1)},
-        "quant_gemm_gather": {"ms": round(ms_full, 4), "tflops": round(flops / (ms_full * 1e-3) / 1e12, 1)},
+        "quant_gemm_gather": {"ms": round(ms_full, 4), "tflops": round(flops / (ms_full * 1e-3) / 1e12, 1),
+                              "exchange": "none (1 GPU)" if world == 1 else
+                              "GEMM epilogue stores into every rank's [M, N] over NVLink (peer memory) + flag wait"},
+        **({"quant_gemm_nccl_gather": {"ms": round(ms_nccl, 4), "tflops": round(flops / (ms_nccl * 1e-3) / 1e12, 1),
+                                       "exchange": "NCCL all-gather of the BF16 slabs after the GEMM"}} if world > 1 else {}),
         "roofline": {"bound": "tensor", "achieved": round(tf / world, 1), "peak": fp4_peak_nominal, "unit": "TFLOP/s",
                      "frac": round(tf / world / fp4_peak_nominal, 4),
                      "traffic": GEMM_DRAM_TRAFFIC_BYTES if world == 1 else None,

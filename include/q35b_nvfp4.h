@@ -221,6 +221,31 @@ Q35B_API int q35b_gemm_w4a4_gate_up_nvfp4(const q35b_weight * w, const uint8_t *
                                           uint8_t * out_codes, uint8_t * out_scales_tiled,
                                           const float * out_scale_dev, unsigned int * status_dev, q35b_stream stream);
 
+/* ---- N-sharded prefill projection with the gather fused into the GEMM's stores ----
+ * Replaces the exchange step of the row-sharded projection (one ncclAllGather of the BF16 slabs after the GEMM):
+ * every rank holds the full output matrix [m, N] in a peer buffer; the GEMM on a shard (q35b_weight_create with
+ * shard_index / shard_count) stores its columns into the local matrix and, with plain peer-memory stores over
+ * NVLink, into every other rank's, and finally writes `epoch` into its flag slot on every rank.
+ * q35b_peer_gather_wait (same stream, after the GEMM) returns once the local slots of all other ranks carry that
+ * epoch, i.e. the whole matrix is in place; its wait is bounded and records 31 in *status_dev on expiry.
+ * Use a new, larger epoch per gathered matrix.  One process per GPU: create the local buffer, pass its handle
+ * (q35b_peer_buffer_handle_bytes() bytes) to the other ranks by any host channel, open theirs.  buffers[world] lists
+ * the mappings by rank, buffers[rank] being the local one.  In one process (tests, several GPUs under one host
+ * thread) created buffers can be listed directly. */
+typedef struct q35b_peer_buffer q35b_peer_buffer;
+Q35B_API int q35b_peer_buffer_create(size_t data_bytes, q35b_peer_buffer ** out);
+Q35B_API size_t q35b_peer_buffer_handle_bytes(void);
+Q35B_API int q35b_peer_buffer_export(const q35b_peer_buffer * buffer, void * handle_out);
+Q35B_API int q35b_peer_buffer_open(const void * handle, size_t data_bytes, q35b_peer_buffer ** out);
+Q35B_API void * q35b_peer_buffer_data(const q35b_peer_buffer * buffer);
+Q35B_API void q35b_peer_buffer_destroy(q35b_peer_buffer * buffer);
+Q35B_API int q35b_gemm_w4a4_bf16_allgather(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
+                                           const float * input_scale_dev, int m, q35b_peer_buffer * const * buffers,
+                                           int world, int rank, int ldc, unsigned int epoch, unsigned int * status_dev,
+                                           q35b_stream stream);
+Q35B_API int q35b_peer_gather_wait(q35b_peer_buffer * const * buffers, int world, int rank, unsigned int epoch,
+                                   unsigned int * status_dev, q35b_stream stream);
+
 /* Prefill projection for callers that cannot allocate device memory (no counterpart in the reference, whose
  * bridges all take caller-allocated scratch, include/qwen35x/runtime/cuda_bench.h:70-83).
  *

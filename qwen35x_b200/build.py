@@ -18,7 +18,7 @@ LIB_DIR = PKG / "_lib"
 LIB = LIB_DIR / "libq35b.so"
 CLI = LIB_DIR / "q35b"
 
-SOURCES = ["api.cu", "gemv_w4a16.cu", "gemv_stream.cu", "act_quant.cu", "gemm_w4a4_tcgen05.cu", "gemm_w4a4_2cta.cu", "static_prefill.cu"]
+SOURCES = ["api.cu", "gemv_w4a16.cu", "gemv_stream.cu", "act_quant.cu", "gemm_w4a4_tcgen05.cu", "gemm_w4a4_2cta.cu", "static_prefill.cu", "peer_gather.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2", "--expt-relaxed-constexpr",
@@ -68,8 +68,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 def build_cli(force: bool = False) -> Path:
     """The C++ host mirror of the reference entry points and its command line (qwen35x_b200/_lib/q35b)."""
     host = CSRC / "host"
-    srcs = [host / "nvfp4_runtime.cpp", host / "q35b_main.cpp"]
-    deps = srcs + [host / "nvfp4_runtime.h", CSRC / "nvfp4_codec.cuh", PKG.parent / "include" / "q35b_nvfp4.h", LIB]
+    srcs = [host / "nvfp4_runtime.cpp", host / "nvfp4_checkpoint.cpp", host / "q35b_main.cpp"]
+    deps = srcs + [host / "nvfp4_runtime.h", host / "nvfp4_checkpoint.h", CSRC / "nvfp4_codec.cuh", PKG.parent / "include" / "q35b_nvfp4.h", LIB]
     if force or _stale(CLI, deps):
         cmd = [_nvcc(), "-std=c++17", "-O2", "-x", "cu", "-gencode", "arch=compute_100a,code=sm_100a", *map(str, srcs),
                "-o", str(CLI), f"-L{LIB_DIR}", "-lq35b", "-Xlinker", "-rpath,$ORIGIN", "-cudart", "static"]

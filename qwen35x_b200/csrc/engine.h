@@ -90,9 +90,19 @@ struct GemmQuantOut {
   uint8_t * scales_tiled;   // tiled block scales of the [m, rows / 2] activation
   const float * g_dev;      // its per-tensor scale, known in advance
 };
+// Where a gathering GEMM repeats its stores on the other ranks and signals completion (see gemm_epilogue.cuh,
+// peer_gather.cu).  Pointers are this process's mappings of the other ranks' buffers, already moved to the shard's
+// first column.
+struct GemmGather {
+  int n_peers = 0;
+  void * peer_c[7] = {};
+  unsigned int * peer_flag[7] = {};
+  unsigned int * done_counter = nullptr;
+  unsigned int epoch = 0;
+};
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
-                     cudaStream_t s, const GemmQuantOut * qout = nullptr);
+                     cudaStream_t s, const GemmQuantOut * qout = nullptr, const GemmGather * gather = nullptr);
 
 
 // gemm_w4a4_2cta.cu

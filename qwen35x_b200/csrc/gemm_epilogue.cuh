@@ -35,7 +35,60 @@ struct GemmEpilogue {
   uint8_t * q_scales = nullptr;
   const float * q_g = nullptr;
   int q_slots = 0;
+  // Gather fused into the stores (multi-GPU, rows sharded): every BF16 store is repeated into the same place of
+  // the full output matrix on each other rank (peer_c[i], plain peer-memory stores over NVLink), and when the whole
+  // grid has stored, its last CTA writes `epoch` into this rank's flag slot on every rank (peer_flag[i]).
+  static constexpr int kMaxPeers = 7;
+  int n_peers = 0;
+  __nv_bfloat16 * peer_c[kMaxPeers] = {};
+  unsigned int * peer_flag[kMaxPeers] = {};
+  unsigned int * done_counter = nullptr;   // this rank's, zero between launches
+  unsigned int epoch = 0;
 };
+
+// A warp that has just stored 32 rows x COLS BF16 columns of the local matrix (one row per lane) sends them to the
+// other ranks as whole lines: it reads its rows back from L2 with eight lanes per 128 bytes and repeats them with the
+// same lane mapping, so every store instruction covers whole 128-byte lines of a few rows, the unit NVLink moves
+// well, instead of thirty-two 32-byte pieces of thirty-two rows.  col0 and n are multiples of 8 (row shards are
+// cut on 128-row boundaries); pieces past column n or row m are skipped.
+template <int COLS>
+__device__ __forceinline__ void gemm_forward_rows_to_peers(const GemmEpilogue & ep, const __nv_bfloat16 * c, int ldc,
+                                                           int row0, int m, int col0, int n, int lane) {
+  constexpr int kPieces = COLS / 8;  // 16-byte pieces per row
+  __threadfence_block();             // the lanes' own stores, before other lanes read them
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < kPieces; ++it) {
+    const int idx = it * 32 + lane;
+    const int row = row0 + idx / kPieces;
+    const int col = col0 + (idx % kPieces) * 8;
+    if (row < m && col + 8 <= n) {
+      const size_t off = static_cast<size_t>(row) * ldc + col;
+      uint4 v;
+      asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(c + off));
+      _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < ep.n_peers) *reinterpret_cast<uint4 *>(ep.peer_c[i] + off) = v;
+    }
+  }
+}
+
+// End of a gathering GEMM kernel; every thread of the CTA calls it after its last output store.
+// A CTA that ran no tiles because an earlier error is recorded (`ran` false) counts itself but the flags are not
+// written then: the other ranks' bounded waits expire and record the failure on their side too.
+__device__ __forceinline__ void gemm_signal_peers(const GemmEpilogue & ep, bool ran) {
+  if (ep.done_counter == nullptr) return;
+  __threadfence_system();  // this thread's stores, local and remote, before anything that follows
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(ep.done_counter, 1u);
+    if (prev == gridDim.x * gridDim.y * gridDim.z - 1) {  // every other CTA fenced its stores before it counted itself
+      *ep.done_counter = 0u;
+      __threadfence_system();
+      if (ran) {
+        _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < ep.n_peers) *reinterpret_cast<volatile unsigned int *>(ep.peer_flag[i]) = ep.epoch;
+      }
+    }
+  }
+}
 
 __device__ __forceinline__ void st_global_v8(void * p, const uint32_t (&v)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
@@ -53,8 +106,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 
 // r: 32 accumulator columns starting at global column col0 (a multiple of 32) of row `row`; n = accumulator columns
 // of the whole problem (weight rows); g = the activation tensor's scale.
+// to_peers: also repeat every store on the other ranks (one 32-byte piece per lane); a caller that forwards whole
+// rows afterwards (gemm_forward_rows_to_peers) passes false.
 __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int row, int col0, int n, float g,
-                                                   const GemmEpilogue & ep, __nv_bfloat16 * __restrict__ c, int ldc) {
+                                                   const GemmEpilogue & ep, __nv_bfloat16 * __restrict__ c, int ldc,
+                                                   bool to_peers = true) {
+  const int n_peers = to_peers ? ep.n_peers : 0;
   const float alpha = g * ep.s2;
   if (ep.gate_up) {
     const float alpha_up = g * ep.s2_up;
@@ -89,13 +146,18 @@ __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int 
         }
       }
       st_global_v8(dst, p);
+      _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < n_peers) st_global_v8(ep.peer_c[i] + static_cast<size_t>(row) * ldc + (col0 >> 1), p);
     } else {
+#pragma unroll
       for (int j = 0; j < 2; ++j) {
+#pragma unroll
         for (int i = 0; i < 8; ++i) {
           if (col0 + 16 * j + 8 + i < n) {
             const float gv = __uint_as_float(r[16 * j + i]) * alpha;
             const float uv = __uint_as_float(r[16 * j + 8 + i]) * alpha_up;
-            dst[8 * j + i] = __float2bfloat16_rn(silu_mul(gv, uv));
+            const __nv_bfloat16 o = __float2bfloat16_rn(silu_mul(gv, uv));
+            dst[8 * j + i] = o;
+            _Pragma("unroll") for (int pi = 0; pi < GemmEpilogue::kMaxPeers; ++pi) if (pi < n_peers) ep.peer_c[pi][static_cast<size_t>(row) * ldc + (col0 >> 1) + 8 * j + i] = o;
           }
         }
       }
@@ -123,12 +185,16 @@ __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int 
                          fmaf(__uint_as_float(r[v * 16 + e * 2 + 1]), alpha, r1));
       }
       st_global_v8(dst + v * 16, p);
+      _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < n_peers) st_global_v8(ep.peer_c[i] + static_cast<size_t>(row) * ldc + col0 + v * 16, p);
     }
   } else {
+#pragma unroll
     for (int e = 0; e < 32; ++e) {
       if (col0 + e < n) {
         const float rv = res != nullptr ? __bfloat162float(res[e]) : 0.0f;
-        dst[e] = __float2bfloat16_rn(fmaf(__uint_as_float(r[e]), alpha, rv));
+        const __nv_bfloat16 o = __float2bfloat16_rn(fmaf(__uint_as_float(r[e]), alpha, rv));
+        dst[e] = o;
+        _Pragma("unroll") for (int pi = 0; pi < GemmEpilogue::kMaxPeers; ++pi) if (pi < n_peers) ep.peer_c[pi][static_cast<size_t>(row) * ldc + col0 + e] = o;
       }
     }
   }

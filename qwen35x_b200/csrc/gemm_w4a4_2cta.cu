@@ -355,13 +355,23 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(drained + ab));
+      // plain BF16 output of a gathering launch: store locally, then forward whole rows; the fused epilogues (and a
+      // launch without peers) store per lane
+      const bool forward = ep.n_peers > 0 && !ep.gate_up;
       if (row < m) {
 #pragma unroll
-        for (int j = 0; j < kEpiCols / 32; ++j) gemm_store_chunk32(r[j], row, tn * kTileN + col_base + 32 * j, n, g, ep, c, ldc);
+        for (int j = 0; j < kEpiCols / 32; ++j) {
+          gemm_store_chunk32(r[j], row, tn * kTileN + col_base + 32 * j, n, g, ep, c, ldc, !forward);
+        }
+      }
+      if (forward) {
+        gemm_forward_rows_to_peers<kEpiCols>(ep, c, ldc, tm * kTileM + static_cast<int>(rank) * kCtaRows + quarter * 32, m,
+                                             tn * kTileN + col_base, n, lane);
       }
     }
   }
 
+  gemm_signal_peers(ep, !aborted);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   cluster_sync();  // neither CTA may leave while its partner can still signal its barriers or read its tiles

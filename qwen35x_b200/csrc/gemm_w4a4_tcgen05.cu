@@ -324,6 +324,7 @@ gemm_w4a4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
   }
 
+  gemm_signal_peers(ep, true);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -404,7 +405,7 @@ int launch_tile(q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_s
 
 int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
-                     cudaStream_t s, const GemmQuantOut * qout) {
+                     cudaStream_t s, const GemmQuantOut * qout, const GemmGather * gather) {
   if (w == nullptr || a_codes == nullptr || a_scales_tiled == nullptr || g_dev == nullptr ||
       (c_bf16 == nullptr && qout == nullptr)) {
     return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection received a null device buffer.");
@@ -435,6 +436,17 @@ int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a
     ep.q_scales = qout->scales_tiled;
     ep.q_g = qout->g_dev;
     ep.q_slots = round_up_int(out_cols / 16, 4);
+  }
+  if (gather != nullptr) {
+    static_assert(sizeof(gather->peer_c) / sizeof(gather->peer_c[0]) == GemmEpilogue::kMaxPeers, "peer table size");
+    if (qout != nullptr || residual_bf16 != nullptr) return fail(Q35B_ERR_ARGUMENT, "The gathering NVFP4 prefill projection takes no residual and writes BF16.");
+    ep.n_peers = gather->n_peers;
+    for (int i = 0; i < gather->n_peers; ++i) {
+      ep.peer_c[i] = static_cast<__nv_bfloat16 *>(gather->peer_c[i]);
+      ep.peer_flag[i] = gather->peer_flag[i];
+    }
+    ep.done_counter = gather->done_counter;
+    ep.epoch = gather->epoch;
   }
   if ((w->k % 64) != 0) return fail(Q35B_ERR_SHAPE, "NVFP4 W4A4 GEMM needs cols to be a multiple of 64.");
   if ((reinterpret_cast<uintptr_t>(a_codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a_scales_tiled) & 15u) != 0) {

@@ -3,10 +3,12 @@
 //   q35b --check-nvfp4-tensor            [--nvfp4-sample-rows N]
 //   q35b --bench-nvfp4-projection        [--nvfp4-projection-kernel row|warp|scale-group|blackwell-fp4|b200-simt|b200-stream]
 //   q35b --bench-nvfp4-prefill-projection [--nvfp4-prefill-seq-len S]
-//        [--bench-warmup W] [--bench-iters K] --synthetic ROWS,COLS[,SEED]
+//        [--bench-warmup W] [--bench-iters K] (--synthetic ROWS,COLS[,SEED] | --hf-model-dir DIR [--nvfp4-tensor BASE])
+//   q35b --validate-nvfp4-model --hf-model-dir DIR [--expect-layers N [--full-attention-interval I]]
 //
-// The reference reads the tensor family from --hf-model-dir/--nvfp4-tensor; no checkpoint reader exists here yet, so
-// the tensor comes from --synthetic (fp32 N(0, 0.02) weights quantised with the engine's NVFP4 recipe).
+// The tensor family comes from a ModelOpt NVFP4 checkpoint directory (--hf-model-dir/--nvfp4-tensor, as in the
+// reference, src/main.cpp:350-385) or from --synthetic (fp32 N(0, 0.02) weights quantised with the engine's NVFP4
+// recipe).  --validate-nvfp4-model applies the checkpoint rules without touching the GPU (src/main.cpp:560-591).
 // Output is the reference's `key: value` block.  Exit codes: 0 ok, 2 usage, 10 failure.
 #include <cmath>
 #include <cstdio>
@@ -15,18 +17,24 @@
 #include <string>
 #include <vector>
 
+#include "nvfp4_checkpoint.h"
 #include "nvfp4_runtime.h"
 
 namespace rt = q35b::runtime;
 
 static void usage() {
   std::cerr << "usage: q35b (--check-nvfp4-tensor | --bench-nvfp4-projection | --bench-nvfp4-prefill-projection)\n"
-               "            --synthetic ROWS,COLS[,SEED] [--nvfp4-projection-kernel NAME] [--nvfp4-sample-rows N]\n"
-               "            [--nvfp4-prefill-seq-len S] [--bench-warmup W] [--bench-iters K] [--nvfp4-input-scale F]\n";
+               "            (--synthetic ROWS,COLS[,SEED] | --hf-model-dir DIR [--nvfp4-tensor BASE])\n"
+               "            [--nvfp4-projection-kernel NAME] [--nvfp4-sample-rows N]\n"
+               "            [--nvfp4-prefill-seq-len S] [--bench-warmup W] [--bench-iters K] [--nvfp4-input-scale F]\n"
+               "       q35b --validate-nvfp4-model --hf-model-dir DIR [--expect-layers N [--full-attention-interval I]]\n";
 }
 
 int main(int argc, char ** argv) {
-  enum Mode { kNone, kCheck, kBench, kPrefill } mode = kNone;
+  enum Mode { kNone, kCheck, kBench, kPrefill, kValidate } mode = kNone;
+  std::string model_dir, tensor_base;
+  int expect_layers = 0, full_interval = 4;
+  bool input_scale_given = false;
   std::string kernel = "scale-group";
   int rows = 0, cols = 0, sample_rows = 16, seq_len = 256, warmup = 5, iters = 20;
   unsigned long long seed = 42;
@@ -48,7 +56,14 @@ int main(int argc, char ** argv) {
     else if (a == "--nvfp4-prefill-seq-len") seq_len = std::atoi(value("--nvfp4-prefill-seq-len"));
     else if (a == "--bench-warmup") warmup = std::atoi(value("--bench-warmup"));
     else if (a == "--bench-iters") iters = std::atoi(value("--bench-iters"));
-    else if (a == "--nvfp4-input-scale") input_scale = static_cast<float>(std::atof(value("--nvfp4-input-scale")));
+    else if (a == "--nvfp4-input-scale") {
+      input_scale = static_cast<float>(std::atof(value("--nvfp4-input-scale")));
+      input_scale_given = true;
+    } else if (a == "--validate-nvfp4-model") mode = kValidate;
+    else if (a == "--hf-model-dir") model_dir = value("--hf-model-dir");
+    else if (a == "--nvfp4-tensor") tensor_base = value("--nvfp4-tensor");
+    else if (a == "--expect-layers") expect_layers = std::atoi(value("--expect-layers"));
+    else if (a == "--full-attention-interval") full_interval = std::atoi(value("--full-attention-interval"));
     else if (a == "--synthetic") {
       const std::string v = value("--synthetic");
       if (std::sscanf(v.c_str(), "%d,%d,%llu", &rows, &cols, &seed) < 2) {
@@ -64,19 +79,63 @@ int main(int argc, char ** argv) {
       return 2;
     }
   }
-  if (mode == kNone || rows <= 0 || cols <= 0) {
+  std::string error;
+  if (mode == kValidate) {
+    if (model_dir.empty()) {
+      std::cerr << "NVFP4 model validation failed: --hf-model-dir is required\n";
+      return 10;
+    }
+    namespace ck = q35b::checkpoint;
+    ck::ValidationResult result;
+    const std::vector<std::string> bases =
+      expect_layers > 0 ? ck::expected_module_bases(expect_layers, full_interval) : std::vector<std::string>();
+    if (!ck::validate_nvfp4_checkpoint(model_dir, bases, result, error)) {
+      std::cerr << "NVFP4 model validation failed: " << error << "\n";
+      return 10;
+    }
+    std::cout << "ModelOpt NVFP4 validation passed\n"
+              << "  model_dir: " << model_dir << "\n"
+              << "  group_size: " << result.group_size << "\n"
+              << "  quantized_modules: " << result.quantized_tensors << "\n"
+              << "  packed_u8_tensors: " << result.packed_u8_tensors << "\n"
+              << "  fp8_scale_tensors: " << result.fp8_scale_tensors << "\n"
+              << "  f32_input_scale_tensors: " << result.f32_input_scale_tensors << "\n"
+              << "  f32_weight_scale2_tensors: " << result.f32_weight_scale2_tensors << "\n";
+    return 0;
+  }
+  const bool from_checkpoint = !model_dir.empty();
+  if (mode == kNone || (!from_checkpoint && (rows <= 0 || cols <= 0))) {
     usage();
     return 2;
   }
 
-  std::string error;
   std::vector<std::uint8_t> packed, scales;
   float s2 = 1.0f;
-  if (!rt::make_synthetic_tensor(rows, cols, seed, 0.02f, packed, scales, s2, error)) {
-    std::cerr << "NVFP4 synthetic tensor failed: " << error << "\n";
-    return 10;
+  std::string tensor;
+  if (from_checkpoint) {
+    // default tensors of the reference's modes (include/qwen35x/runtime/runtime.h:31,56,76)
+    if (tensor_base.empty()) {
+      tensor_base = mode == kCheck ? "model.language_model.layers.0.linear_attn.in_proj_qkv" : "model.language_model.layers.0.mlp.gate_proj";
+    }
+    q35b::checkpoint::Nvfp4Tensor t;
+    if (!q35b::checkpoint::load_nvfp4_tensor(model_dir, tensor_base, t, error)) {
+      std::cerr << "NVFP4 tensor load failed: " << error << "\n";
+      return 10;
+    }
+    packed = std::move(t.packed_weights);
+    scales = std::move(t.weight_scales);
+    s2 = t.weight_scale_2;
+    rows = t.rows;
+    cols = t.cols;
+    if (!input_scale_given) input_scale = t.input_scale;
+    tensor = tensor_base;
+  } else {
+    if (!rt::make_synthetic_tensor(rows, cols, seed, 0.02f, packed, scales, s2, error)) {
+      std::cerr << "NVFP4 synthetic tensor failed: " << error << "\n";
+      return 10;
+    }
+    tensor = "synthetic[" + std::to_string(rows) + "," + std::to_string(cols) + "] seed " + std::to_string(seed);
   }
-  const std::string tensor = "synthetic[" + std::to_string(rows) + "," + std::to_string(cols) + "] seed " + std::to_string(seed);
 
   if (mode == kCheck) {
     double max_abs_error = 0.0;

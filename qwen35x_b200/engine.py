@@ -86,6 +86,22 @@ def lib() -> C.CDLL:
     L.q35b_project_prefill_bf16_static.argtypes = [vp, vp, i, f, vp, i, vp]
     L.q35b_gemm_w4a4_bf16_residual.restype = i
     L.q35b_gemm_w4a4_bf16_residual.argtypes = [vp, vp, vp, vp, i, vp, i, vp, i, vp, vp]
+    L.q35b_peer_buffer_create.restype = i
+    L.q35b_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(vp)]
+    L.q35b_peer_buffer_handle_bytes.restype = C.c_size_t
+    L.q35b_peer_buffer_handle_bytes.argtypes = []
+    L.q35b_peer_buffer_export.restype = i
+    L.q35b_peer_buffer_export.argtypes = [vp, vp]
+    L.q35b_peer_buffer_open.restype = i
+    L.q35b_peer_buffer_open.argtypes = [vp, C.c_size_t, C.POINTER(vp)]
+    L.q35b_peer_buffer_data.restype = vp
+    L.q35b_peer_buffer_data.argtypes = [vp]
+    L.q35b_peer_buffer_destroy.restype = None
+    L.q35b_peer_buffer_destroy.argtypes = [vp]
+    L.q35b_gemm_w4a4_bf16_allgather.restype = i
+    L.q35b_gemm_w4a4_bf16_allgather.argtypes = [vp, vp, vp, vp, i, C.POINTER(vp), i, i, i, C.c_uint, vp, vp]
+    L.q35b_peer_gather_wait.restype = i
+    L.q35b_peer_gather_wait.argtypes = [C.POINTER(vp), i, i, C.c_uint, vp, vp]
     L.q35b_gemm_w4a4_gate_up_nvfp4.restype = i
     L.q35b_gemm_w4a4_gate_up_nvfp4.argtypes = [vp, vp, vp, vp, i, vp, vp, vp, vp, vp]
     L.q35b_debug_encode_ue4m3.restype = C.c_uint8
@@ -373,6 +389,83 @@ def gemm_w4a4_gate_up_quant(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: 
                                               codes.data_ptr(), scales.data_ptr(), out_scale.data_ptr(), st,
                                               _stream_ptr(torch)))
     return codes.view(m, inter // 2), scales, out_scale
+
+
+class PeerBuffer:
+    """One rank's full output matrix [m, n] BF16 in memory the other ranks can store into (q35b_peer_buffer_*):
+    `PeerBuffer.create(m, n)` on the owning rank, `export()` -> bytes for the other ranks, `PeerBuffer.open(handle, m, n)`
+    there.  `tensor()` views the matrix as a torch tensor (owner and openers alike)."""
+
+    def __init__(self, handle, m: int, n: int, device):
+        self._h = handle
+        self.m, self.n, self.device = m, n, device
+
+    @classmethod
+    def create(cls, m: int, n: int) -> "PeerBuffer":
+        torch = _torch()
+        h = C.c_void_p()
+        _check(lib().q35b_peer_buffer_create(m * n * 2, C.byref(h)))
+        return cls(h, m, n, torch.device("cuda", torch.cuda.current_device()))
+
+    @classmethod
+    def open(cls, handle: bytes, m: int, n: int) -> "PeerBuffer":
+        torch = _torch()
+        assert len(handle) == int(lib().q35b_peer_buffer_handle_bytes())
+        h = C.c_void_p()
+        buf = C.create_string_buffer(handle, len(handle))
+        _check(lib().q35b_peer_buffer_open(buf, m * n * 2, C.byref(h)))
+        return cls(h, m, n, torch.device("cuda", torch.cuda.current_device()))
+
+    def export(self) -> bytes:
+        buf = C.create_string_buffer(int(lib().q35b_peer_buffer_handle_bytes()))
+        _check(lib().q35b_peer_buffer_export(self._h, buf))
+        return buf.raw
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def __cuda_array_interface__(self):
+        return {"shape": (self.m, self.n), "typestr": "<u2", "data": (int(lib().q35b_peer_buffer_data(self._h)), False),
+                "version": 3, "strides": None}
+
+    def tensor(self):
+        torch = _torch()
+        return torch.as_tensor(self, device=self.device).view(torch.bfloat16)
+
+    def close(self) -> None:
+        if self._h:
+            lib().q35b_peer_buffer_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def gemm_w4a4_allgather(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, buffers, rank: int, epoch: int, status,
+                        wait: bool = True):
+    """The shard's GEMM storing into every rank's matrix (buffers: PeerBuffer per rank, buffers[rank] local), then
+    (wait=True) the bounded wait for the other ranks' parts; after it, buffers[rank].tensor() holds the whole [m, n]."""
+    torch = _torch()
+    world = len(buffers)
+    arr = (C.c_void_p * world)(*[b.handle for b in buffers])
+    assert status is not None and status.is_cuda
+    _check(lib().q35b_gemm_w4a4_bf16_allgather(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(), g.data_ptr(), m,
+                                               arr, world, rank, buffers[rank].n, epoch, status.data_ptr(), _stream_ptr(torch)))
+    if wait:
+        peer_gather_wait(buffers, rank, epoch, status)
+
+
+def peer_gather_wait(buffers, rank: int, epoch: int, status) -> None:
+    """Bounded device-side wait until every other rank's part of epoch `epoch` is in buffers[rank]."""
+    torch = _torch()
+    world = len(buffers)
+    arr = (C.c_void_p * world)(*[b.handle for b in buffers])
+    _check(lib().q35b_peer_gather_wait(arr, world, rank, epoch, status.data_ptr(), _stream_ptr(torch)))
 
 
 def project_prefill(weight: Nvfp4Weight, x, out=None, scratch=None, global_scale: float = 0.0, residual=None):

@@ -66,3 +66,52 @@ def assemble(gathered, n: int):
     for (begin, count), slab in zip(shard_layout(n, world), gathered):
         out[:, begin:begin + count] = slab[:, :count]
     return out
+
+
+class PeerGather:
+    """The exchange step fused into the GEMM's stores (q35b_gemm_w4a4_bf16_allgather): every rank owns a full
+    [m, n] BF16 matrix the others can store into; handles travel once through the process group at construction.
+
+        gather = PeerGather(m, n)                       # collective: every rank of the group calls it
+        gather.project(weight_shard, codes, scales, g)  # GEMM + stores to all ranks + bounded wait
+        c = gather.tensor()                             # [m, n] on this rank
+
+    Ranks must call `project` the same number of times (each call is one epoch).  Before reusing the matrix for the
+    next projection every rank must have finished reading it: call `dist.barrier()` or order the work otherwise."""
+
+    def __init__(self, m: int, n: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        from . import engine
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.m, self.n = m, n
+        self.local = engine.PeerBuffer.create(m, n)
+        mine = torch.frombuffer(bytearray(self.local.export()), dtype=torch.uint8).cuda()
+        handles = torch.empty((self.world, mine.numel()), dtype=torch.uint8, device=mine.device)
+        dist.all_gather_into_tensor(handles, mine, group=group)
+        handles = handles.cpu().numpy()
+        self.buffers = [self.local if r == self.rank else engine.PeerBuffer.open(handles[r].tobytes(), m, n)
+                        for r in range(self.world)]
+        self.status = torch.zeros(1, dtype=torch.int32, device=mine.device)
+        self.epoch = 0
+        dist.barrier(group)
+
+    def project(self, weight_shard, a_codes, a_scales_tiled, g):
+        from . import engine
+
+        self.epoch += 1
+        engine.gemm_w4a4_allgather(weight_shard, a_codes, a_scales_tiled, g, self.m, self.buffers, self.rank, self.epoch,
+                                   self.status)
+        return self.local.tensor()
+
+    def tensor(self):
+        return self.local.tensor()
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code != 0:
+            raise RuntimeError(f"device-side wait expired in the gathering projection, code {code}")
