@@ -59,3 +59,31 @@ def test_no_cpu_fallback(engine):
 
     with pytest.raises(engine.Q35bError):
         engine.Nvfp4Weight.from_host(np.zeros((8, 8), np.uint8), np.zeros((8, 1), np.uint8), 1.0)
+
+
+def test_shape_report_renders_markdown():
+    """The per-shape report's table renderer (no GPU): every section of a report dict appears with its rows."""
+    from qwen35x_b200 import shape_report
+
+    gemm = {"us": 10.0, "TFLOP/s": 100.0, "fp4_nominal_frac": 0.011, "frac_of_4x_measured_bf16": 0.015}
+    report = {
+        "peaks": {"hbm_gbs": 6545.0, "bf16_tflops": 1699.0},
+        "decode": [{"workload": "step", "M": 1, "projections": 96, "bytes": 234578304, "us": 50.0, "GB/s": 4691.6,
+                    "hbm_frac": 0.7168, "kernel": "gemv_w4a16_stream_kernel (work list)"}],
+        "single_projection": [{"workload": "one", "M": 1, "N": 3584, "K": 1024, "bytes": 2073604, "us": 5.0, "GB/s": 414.7,
+                               "hbm_frac": 0.063, "kernel": "gemv_w4a16_simt_kernel", "l2": "96 weight copies rotated"}],
+        "sweep_decode": [],
+        "prefill": [{"workload": "gemm", "M": 512, "N": 18432, "K": 2560, "GFLOP": 48.3, "gemm_only": gemm,
+                     "quant_gemm": gemm, "kernel": "gemm_w4a4_2cta_kernel"}],
+        "sweep_prefill": [],
+        "prefill_mlp": [{"workload": "mlp", "M": 4096, "hidden": 2560, "intermediate": 9216, "GFLOP": 579.8,
+                         "bf16_intermediate_then_quantise": {"us": 248.3, "TFLOP/s": 2335.1},
+                         "nvfp4_intermediate_from_epilogue": {"us": 205.4, "TFLOP/s": 2823.4}}],
+        "cpu_reference": [{"N": 3584, "K": 1024, "M": 1, "cpu_us_1_thread_extrapolated": 39418.5,
+                           "cpu_us_16_threads_extrapolated": 4599.8, "cores": 16, "sample": "1024 rows"}],
+    }
+    md = shape_report.to_markdown(report)
+    for needle in ("| step | 1 | 96 | 234.6 | 50.00 | 4691.6 | 0.717 | `gemv_w4a16_stream_kernel` |", "| one | 1 | 3584 | 1024 |",
+                   "| gemm | 512 | 18432 | 2560 | 48.3 | 10.00 | 100.0 | 0.011 | 0.015 | 10.00 | `gemm_w4a4_2cta_kernel` |",
+                   "| mlp | 4096 | 2560 | 9216 | 579.8 | 248.30 | 2335.1 | 205.40 | 2823.4 |", "| (3584, 1024, 1) | 39418 | 4600 | 16 | 1024 rows |"):
+        assert needle in md, needle
