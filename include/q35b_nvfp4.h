@@ -135,10 +135,13 @@ Q35B_API int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, in
 Q35B_API int q35b_gemv_w4a16_f32(const q35b_weight * w, const float * x_f32, float input_scale, float * y_f32,
                                  int kernel, q35b_stream stream);
 
-/* One persistent launch over several independent projections (the work list of a decode step, or of one phase of
- * it).  Replaces the per-phase matvec loops of the reference's persistent decode kernel
+/* One persistent launch over several projections (the work list of a decode step, or of one phase of it).
+ * Replaces the per-phase matvec loops of the reference's persistent decode kernel
  * (src/kernels/cuda/decode_kernel.cuh:58-84).  Every weight needs cols % 256 == 0 and unsigned block scales.
- * The items are independent: no projection may read another one's output in the same run. */
+ * Items are independent unless one names an earlier item in `after`: then its x_bf16 may be that item's y_bf16 (the
+ * down projection reading the gate/up output), and the kernel holds its activations back until every tile of the
+ * earlier item has been stored -- where the reference's decode kernel puts a grid-wide barrier between the two
+ * phases (decode_kernel.cuh:76-84), with a bounded wait instead of an unbounded one. */
 typedef struct q35b_gemv_item {
   const q35b_weight * weight;
   const void * x_bf16;        /* [m, K] device */
@@ -146,6 +149,7 @@ typedef struct q35b_gemv_item {
   const void * residual_bf16; /* NULL, or [m, rows] device: y = bf16(projection + residual), the fused epilogue of
                                  matvec_down_residual_nvfp4 / matvec_o_residual_nvfp4
                                  (src/kernels/cuda/decode_layers.cuh:404-428, 465-489) */
+  int after;                  /* 0: independent; k > 0: runs after item k - 1 of the same list (k - 1 < own index) */
 } q35b_gemv_item;
 
 typedef struct q35b_gemv_batch q35b_gemv_batch;

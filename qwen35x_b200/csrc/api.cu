@@ -279,7 +279,7 @@ int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void
     auto * wm = const_cast<q35b_weight *>(w);
     if (wm->stream_batch[m] == nullptr) {
       // first use with this token count: build (and upload) the single-projection work list
-      q35b_gemv_item item{w, nullptr, nullptr, nullptr};
+      q35b_gemv_item item{w, nullptr, nullptr, nullptr, 0};
       if (const int st = gemv_batch_build(&item, 1, m, &wm->stream_batch[m])) return st;
     }
     return gemv_batch_launch(wm->stream_batch[m], x_bf16, y_bf16, static_cast<cudaStream_t>(stream));

@@ -57,7 +57,7 @@ constexpr int kXPad = 16;                       // fp16 elements of padding betw
 
 enum Epilogue : int { kEpiPlain = 0, kEpiGateUp = 1 };
 
-enum StatusCode : unsigned { kProducerWait = 11, kPrepWait = 12, kConsumerWait = 13, kConsumerXWait = 14 };
+enum StatusCode : unsigned { kProducerWait = 11, kPrepWait = 12, kConsumerWait = 13, kConsumerXWait = 14, kDependencyWait = 15 };
 
 struct alignas(128) GemvItem {
   CUtensorMap tmap;              // codes [rows, K/2], box 128 rows x 128 bytes, 128B swizzle
@@ -86,6 +86,9 @@ struct alignas(16) GemvTile {
   const __nv_bfloat16 * residual;  // NULL or [m, rows]: added before the BF16 rounding
   float s2_up;                     // gate/up weight: weight_scale_2 of the up rows
   int epilogue;                    // kEpiPlain | kEpiGateUp
+  int wait_item;                   // -1, or the item whose output this item's activations are
+  unsigned int wait_count;         // completions that item reports per run (its tiles x 8 storing warps)
+  int signal;                      // nonzero: another item waits for this one, count every stored tile part
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -171,7 +174,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * __restrict__ tiles,
                          const int * __restrict__ cta_begin, int m_tokens, const __nv_bfloat16 * x_override,
                          __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
-                         int x_raw_bytes, int x_raw_depth, int x_bufs, unsigned int * status) {
+                         int x_raw_bytes, int x_raw_depth, int x_bufs, unsigned long long * item_done,
+                         int counted_items, unsigned int * status) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled code tiles; pointer arithmetic on the __shared__ array (rather than an
   // integer round trip) keeps every later access a shared-memory access for the compiler.
@@ -261,14 +265,46 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       while (ti < n_tiles && tile_at(ti)->item == prev) ++ti;
       return ti;
     };
+    // An item that runs after another one may read its activations only when every storing warp of every tile of
+    // that item has counted itself in item_done (stores fenced before the count).  `block` false: just look.
+    auto dependency_met = [&](const GemvTile * tl, bool block) -> bool {
+      if (tl->wait_item < 0) return true;
+      int met = 0;
+      if (lane == 0) {
+        const volatile unsigned long long * cnt = item_done + tl->wait_item;
+        for (uint32_t i = 0; i < kWaitLimit; ++i) {
+          if (*cnt >= tl->wait_count) {
+            met = 1;
+            break;
+          }
+          if (!block) break;
+          __nanosleep(32);
+        }
+      }
+      met = __shfl_sync(0xffffffffu, met, 0);
+      if (met) {
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");  // the bulk copy that follows reads what other SMs stored
+      }
+      return met != 0;
+    };
     int issue_ti = next_run(0, -1);
     uint32_t issued = 0;
     int proc_ti = issue_ti;
     uint32_t xi = 0;
-    while (proc_ti < n_tiles) {
-      // keep up to x_raw_depth raw copies in flight (none when the plan has no room for a raw ring)
+    bool prep_ok = true;
+    while (proc_ti < n_tiles && prep_ok) {
+      // keep up to x_raw_depth raw copies in flight (none when the plan has no room for a raw ring); a copy whose
+      // source is not complete yet is not issued ahead of time, only when its turn to be converted has come
       while (x_raw_depth > 0 && issue_ti < n_tiles && issued < xi + static_cast<uint32_t>(x_raw_depth)) {
         const GemvTile * tl = tile_at(issue_ti);
+        if (!dependency_met(tl, issue_ti == proc_ti)) {
+          if (issue_ti == proc_ti) {
+            if (lane == 0) atomicExch(status, kDependencyWait);
+            prep_ok = false;
+          }
+          break;
+        }
         if (lane == 0) {
           const uint32_t rb = issued % x_raw_depth;
           const uint32_t bytes = static_cast<uint32_t>(m_tokens) * tl->k * 2u;
@@ -279,7 +315,12 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         ++issued;
         issue_ti = next_run(issue_ti + 1, tl->item);
       }
+      if (!prep_ok) break;
       const GemvTile * tile = tile_at(proc_ti);
+      if (x_raw_depth == 0 && !dependency_met(tile, true)) {
+        if (lane == 0) atomicExch(status, kDependencyWait);
+        break;
+      }
       const int buf = (x_bufs == 2) ? (xi & 1) : 0;
       const uint32_t xphase = (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1);
       const uint32_t rb = x_raw_depth > 0 ? xi % x_raw_depth : 0;
@@ -530,11 +571,30 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
             }
           }
         }
+        if (tile->signal) {
+          // another item of this run reads these outputs: make the stores visible, then count this warp's part
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(item_done + tile->item, 1ULL);
+        }
       }
     }
     if (ok && prev_item >= 0) {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(xempty + buf));
+    }
+  }
+  if (counted_items > 0) {
+    // A run with dependencies leaves its completion counts at zero for the next one: the last CTA to get here clears
+    // them (every wait of the run has ended by then, since every CTA is past its last tile).
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int * ctas_done = reinterpret_cast<unsigned int *>(item_done + counted_items);
+      __threadfence();
+      if (atomicAdd(ctas_done, 1u) == gridDim.x - 1) {
+        for (int i = 0; i < counted_items; ++i) item_done[i] = 0ULL;
+        *ctas_done = 0u;
+      }
     }
   }
 }
@@ -597,6 +657,8 @@ struct q35b_gemv_batch {
   GemvTile * tiles = nullptr;
   int * cta_begin = nullptr;
   unsigned int * status = nullptr;
+  unsigned long long * item_done = nullptr;  // per item: storing warps that finished a tile in the current run
+  bool has_dependencies = false;
   size_t bytes_per_run = 0;
 };
 
@@ -623,6 +685,9 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
     }
     if ((reinterpret_cast<uintptr_t>(items[i].x_bf16) & 15u) != 0) {
       return fail(Q35B_ERR_ARGUMENT, "Activations of the NVFP4 projection work list must be 16-byte aligned.");
+    }
+    if (items[i].after < 0 || items[i].after > i) {
+      return fail(Q35B_ERR_ARGUMENT, "An NVFP4 projection work list item can only run after an earlier item of the list.");
     }
     max_k = std::max(max_k, w->k);
   }
@@ -670,9 +735,26 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
       tl.residual = static_cast<const __nv_bfloat16 *>(items[i].residual_bf16);
       tl.s2_up = w->s2_up;
       tl.epilogue = w->gate_up ? kEpiGateUp : kEpiPlain;
+      tl.wait_item = items[i].after - 1;
+      tl.wait_count = 0;
+      tl.signal = 0;
+      if (tl.wait_item >= 0) {
+        const q35b_weight * dep = items[tl.wait_item].weight;
+        tl.wait_count = static_cast<unsigned int>((dep->rows + kTileRows - 1) / kTileRows) * kRowGroups;
+        b->has_dependencies = true;
+      }
+      for (int j = i + 1; j < count; ++j) {
+        if (items[j].after - 1 == i) tl.signal = 1;
+      }
       all.push_back(tl);
     }
     b->bytes_per_run += w->codes_bytes + w->scales_bytes;
+  }
+  std::vector<int> level(count, 0);
+  int max_level = 0;
+  for (int i = 0; i < count; ++i) {
+    if (items[i].after > 0) level[i] = level[items[i].after - 1] + 1;
+    max_level = std::max(max_level, level[i]);
   }
   const int grid = std::max(1, std::min<int>(grid_max, static_cast<int>(all.size())));
   std::vector<std::vector<GemvTile>> per_cta(grid);
@@ -681,21 +763,28 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
     // and therefore converts a new activation vector, as rarely as possible, and neighbouring CTAs stream
     // neighbouring rows.  A tile goes to the CTA in whose share of the total cost its midpoint falls, so no CTA
     // exceeds its share by more than half a tile.
-    long total = 0;
-    for (const GemvTile & tl : all) total += tl.k_steps + 1;
-    long done = 0;
-    int c = 0;
-    for (const GemvTile & tl : all) {
-      const long cost = tl.k_steps + 1;
-      while (c + 1 < grid && (done + cost / 2) * grid >= static_cast<long>(c + 1) * total) ++c;
-      per_cta[c].push_back(tl);
-      done += cost;
+    // With dependencies the list is cut into levels (an item's level is one more than that of the item it runs
+    // after): every level is spread over all CTAs in this way by itself, and a CTA walks its levels in order, so the
+    // whole grid works on the tiles something is waiting for instead of a few CTAs owning them.
+    for (int lv = 0; lv <= max_level; ++lv) {
+      long total = 0;
+      for (const GemvTile & tl : all) total += level[tl.item] == lv ? tl.k_steps + 1 : 0;
+      long done = 0;
+      int c = 0;
+      for (const GemvTile & tl : all) {
+        if (level[tl.item] != lv) continue;
+        const long cost = tl.k_steps + 1;
+        while (c + 1 < grid && (done + cost / 2) * grid >= static_cast<long>(c + 1) * total) ++c;
+        per_cta[c].push_back(tl);
+        done += cost;
+      }
     }
   }
   std::vector<GemvTile> h_tiles;
   std::vector<int> h_begin(grid + 1, 0);
   for (int c = 0; c < grid; ++c) {
-    std::stable_sort(per_cta[c].begin(), per_cta[c].end(), [](const GemvTile & a, const GemvTile & d) {
+    std::stable_sort(per_cta[c].begin(), per_cta[c].end(), [&](const GemvTile & a, const GemvTile & d) {
+      if (level[a.item] != level[d.item]) return level[a.item] < level[d.item];
       return a.item != d.item ? a.item < d.item : a.row_block < d.row_block;
     });
     h_begin[c] = static_cast<int>(h_tiles.size());
@@ -707,7 +796,8 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
   const size_t o_tiles = sizeof(GemvItem) * count;
   const size_t o_begin = (o_tiles + sizeof(GemvTile) * h_tiles.size() + 15) / 16 * 16;
   const size_t o_status = (o_begin + sizeof(int) * (grid + 1) + 15) / 16 * 16;
-  const size_t total = o_status + 16;
+  const size_t o_done = o_status + 16;
+  const size_t total = o_done + sizeof(unsigned long long) * (count + 1);  // + the finished-CTA count
   cudaError_t e = cudaMalloc(&b->dev_base, total);
   if (e != cudaSuccess) {
     delete b;
@@ -718,10 +808,11 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
   b->tiles = reinterpret_cast<GemvTile *>(base + o_tiles);
   b->cta_begin = reinterpret_cast<int *>(base + o_begin);
   b->status = reinterpret_cast<unsigned int *>(base + o_status);
+  b->item_done = reinterpret_cast<unsigned long long *>(base + o_done);
   e = cudaMemcpy(b->items, h_items.data(), sizeof(GemvItem) * count, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(b->tiles, h_tiles.data(), sizeof(GemvTile) * h_tiles.size(), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(b->cta_begin, h_begin.data(), sizeof(int) * (grid + 1), cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = cudaMemset(b->status, 0, 16);
+  if (e == cudaSuccess) e = cudaMemset(b->status, 0, 16 + sizeof(unsigned long long) * (count + 1));
   if (e == cudaSuccess) {
     e = cudaFuncSetAttribute(gemv_w4a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
   }
@@ -741,14 +832,15 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   if (b == nullptr) return fail(Q35B_ERR_ARGUMENT, "Null NVFP4 projection work list.");
   const auto * xo = static_cast<const __nv_bfloat16 *>(x_override);
   auto * yo = static_cast<__nv_bfloat16 *>(y_override);
+  const int counted = b->has_dependencies ? b->count : 0;
   if (b->m <= 4) {
     gemv_w4a16_stream_kernel<1><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
       b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
-      b->plan.x_raw_depth, b->plan.x_bufs, b->status);
+      b->plan.x_raw_depth, b->plan.x_bufs, b->item_done, counted, b->status);
   } else {
     gemv_w4a16_stream_kernel<2><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
       b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
-      b->plan.x_raw_depth, b->plan.x_bufs, b->status);
+      b->plan.x_raw_depth, b->plan.x_bufs, b->item_done, counted, b->status);
   }
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "gemv_w4a16_stream_kernel launch");

@@ -249,15 +249,17 @@ def gemv_w4a16_f32(weight: Nvfp4Weight, x, input_scale: float = 1.0, out=None, k
 
 
 class _GemvItem(C.Structure):
-    _fields_ = [("weight", C.c_void_p), ("x_bf16", C.c_void_p), ("y_bf16", C.c_void_p), ("residual_bf16", C.c_void_p)]
+    _fields_ = [("weight", C.c_void_p), ("x_bf16", C.c_void_p), ("y_bf16", C.c_void_p), ("residual_bf16", C.c_void_p),
+                ("after", C.c_int)]
 
 
 class GemvBatch:
-    """A prepared work list of independent decode projections run by one persistent launch
-    (q35b_gemv_batch_* in include/q35b_nvfp4.h).  items: sequence of (Nvfp4Weight, x [m,K] bf16, y [m,out_rows] bf16)
-    or (weight, x, y, residual [m,rows] bf16): with a residual the projection is added to it before the BF16 rounding;
-    a gate/up weight (Nvfp4Weight.gate_up_from_host) yields silu(gate)*up with out_rows = rows/2.
-    The tensors must stay alive and in place for the life of the batch."""
+    """A prepared work list of decode projections run by one persistent launch (q35b_gemv_batch_* in
+    include/q35b_nvfp4.h).  items: sequence of (Nvfp4Weight, x [m,K] bf16, y [m,out_rows] bf16),
+    (weight, x, y, residual [m,rows] bf16) or (weight, x, y, residual-or-None, after): with a residual the projection
+    is added to it before the BF16 rounding; a gate/up weight (Nvfp4Weight.gate_up_from_host) yields silu(gate)*up
+    with out_rows = rows/2; `after` = index of an earlier item whose y this item's x is (the down projection after
+    gate/up) -- items without it are independent.  The tensors must stay alive and in place for the life of the batch."""
 
     def __init__(self, items, m: int):
         torch = _torch()
@@ -266,12 +268,15 @@ class GemvBatch:
         for j, item in enumerate(self._keep):
             w, x, y = item[0], item[1], item[2]
             res = item[3] if len(item) > 3 else None
+            after = item[4] if len(item) > 4 and item[4] is not None else -1
+            assert -1 <= after < j
             out_rows = w.rows // 2 if w.gate_up else w.rows
             assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and tuple(x.shape) == (m, w.k)
             assert y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and tuple(y.shape) == (m, out_rows)
             if res is not None:
                 assert res.is_cuda and res.dtype == torch.bfloat16 and res.is_contiguous() and tuple(res.shape) == (m, w.rows)
-            arr[j] = _GemvItem(w.handle.value, x.data_ptr(), y.data_ptr(), res.data_ptr() if res is not None else None)
+            arr[j] = _GemvItem(w.handle.value, x.data_ptr(), y.data_ptr(), res.data_ptr() if res is not None else None,
+                               after + 1)
         h = C.c_void_p()
         _check(lib().q35b_gemv_batch_create(arr, len(self._keep), m, C.byref(h)))
         self._h = h

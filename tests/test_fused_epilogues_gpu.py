@@ -212,3 +212,73 @@ def test_prefill_gate_up_to_nvfp4_rejects(engine):
     with pytest.raises(engine.Q35bError) as e:
         engine.gemm_w4a4_gate_up_quant(odd, a_codes, a_scales, g, 8, one)
     assert e.value.status == 2
+
+
+@pytest.mark.parametrize("m", [1, 4])
+def test_work_list_with_dependencies(engine, oracle, m):
+    """Two MLP blocks chained in ONE launch: gate/up -> down(+residual) -> gate/up -> down(+residual); each item
+    names the item whose output it reads, and the kernel holds its activations back until that item is stored.
+    Replayed through a CUDA graph to check that the completion counts are reset per run."""
+    import torch
+
+    hidden, inter = 1024, 3584
+    weights, items, expect = [], [], []
+    x0 = make_activations(m, hidden, seed=70)
+    x_host = oracle.bf16_to_f32(x0)
+    x_dev = to_torch_bf16(x0)
+    cur_dev, cur_bits = x_dev, x0
+    for layer in range(2):
+        _, g_codes, g_scales, g_s2 = make_weight(inter, hidden, seed=71 + 3 * layer, std=0.05)
+        _, u_codes, u_scales, u_s2 = make_weight(inter, hidden, seed=72 + 3 * layer, std=0.03)
+        _, d_codes, d_scales, d_s2 = make_weight(hidden, inter, seed=73 + 3 * layer, std=0.05)
+        gu = engine.Nvfp4Weight.gate_up_from_host(g_codes, g_scales, g_s2, u_codes, u_scales, u_s2)
+        down = engine.Nvfp4Weight.from_host(d_codes, d_scales, d_s2)
+        weights += [gu, down]
+        h = torch.zeros((m, inter), dtype=torch.bfloat16, device="cuda")
+        y = torch.zeros((m, hidden), dtype=torch.bfloat16, device="cuda")
+        items.append((gu, cur_dev, h, None, len(items) - 1 if layer > 0 else None))
+        items.append((down, h, y, cur_dev, len(items) - 1))
+        # oracle chain on the BF16 values the kernel sees
+        _, gate = oracle.gemv_bf16(g_codes, g_scales, g_s2, cur_bits, threads=8)
+        _, up = oracle.gemv_bf16(u_codes, u_scales, u_s2, cur_bits, threads=8)
+        h_bits = oracle.bf16_round((gate / (np.float32(1.0) + np.exp(-gate, dtype=np.float32)) * up).astype(np.float32))
+        _, d = oracle.gemv_bf16(d_codes, d_scales, d_s2, h_bits, threads=8)
+        y_bits = oracle.bf16_round(d + oracle.bf16_to_f32(cur_bits))
+        expect.append((h, h_bits, y, y_bits))
+        cur_dev, cur_bits = y, y_bits
+    del x_host
+    batch = engine.GemvBatch(items, m)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        batch.run()
+        stream.synchronize()
+        assert batch.status() == 0
+        first = [t[2].clone() for t in expect]
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            batch.run()
+        for t in expect:
+            t[0].zero_()
+            t[2].zero_()
+        for _ in range(3):
+            graph.replay()
+        stream.synchronize()
+    assert batch.status() == 0
+    for (h, h_bits, y, y_bits), y_first in zip(expect, first):
+        assert torch.equal(y, y_first)
+        assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(h)), oracle.bf16_to_f32(h_bits)) <= 2 * REL_L2_TOL
+        assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(y)), oracle.bf16_to_f32(y_bits)) <= 2 * REL_L2_TOL
+
+
+def test_work_list_dependency_must_point_backwards(engine):
+    import torch
+
+    _, codes, scales, s2 = make_weight(256, 256, seed=1)
+    w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+    x = torch.zeros((1, 256), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((1, 256), dtype=torch.bfloat16, device="cuda")
+    arr = (engine.engine._GemvItem * 1)(engine.engine._GemvItem(w.handle.value, x.data_ptr(), y.data_ptr(), None, 1))
+    import ctypes
+
+    h = ctypes.c_void_p()
+    assert engine.lib().q35b_gemv_batch_create(arr, 1, 1, ctypes.byref(h)) == 1  # item 0 cannot run after item 0
