@@ -196,6 +196,12 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   uint64_t * red_free = red_full + 2;
   uint64_t * xraw_full = red_free + 2;
 
+  // Programmatic dependent launch: the next kernel of the stream may start on an SM as soon as this kernel's CTA has
+  // left it, and this kernel may start under the tail of the previous one.  Weights, tile descriptors and tensor
+  // maps are constant for the life of the work list, so the producer streams them at once; whatever an earlier
+  // kernel may have written (activations, residuals, completion counts) and every output store comes after
+  // griddepcontrol.wait, which returns when all earlier work of the stream is complete and visible.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tile_begin = cta_begin[blockIdx.x];
@@ -288,6 +294,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       }
       return met != 0;
     };
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     int issue_ti = next_run(0, -1);
     uint32_t issued = 0;
     int proc_ti = issue_ti;
@@ -422,6 +429,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           ok = false;
           break;
         }
+        if (xi == 0) asm volatile("griddepcontrol.wait;" ::: "memory");  // returns at once: the activation warp has waited
         ++xi;
       }
       const int k_steps = tile->k_steps;
@@ -833,17 +841,25 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   const auto * xo = static_cast<const __nv_bfloat16 *>(x_override);
   auto * yo = static_cast<__nv_bfloat16 *>(y_override);
   const int counted = b->has_dependencies ? b->count : 0;
-  if (b->m <= 4) {
-    gemv_w4a16_stream_kernel<1><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
-      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
-      b->plan.x_raw_depth, b->plan.x_bufs, b->item_done, counted, b->status);
-  } else {
-    gemv_w4a16_stream_kernel<2><<<b->grid, kThreads, b->plan.smem_bytes, s>>>(
-      b->items, b->tiles, b->cta_begin, b->m, xo, yo, b->plan.stages, b->plan.x_buf_halfs, b->plan.xs_buf_floats, b->plan.x_raw_bytes,
-      b->plan.x_raw_depth, b->plan.x_bufs, b->item_done, counted, b->status);
-  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(b->grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(b->plan.smem_bytes);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const GemvItem * d_items = b->items;
+  const GemvTile * d_tiles = b->tiles;
+  const int * d_begin = b->cta_begin;
+  const Plan & pl = b->plan;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, b->m <= 4 ? gemv_w4a16_stream_kernel<1> : gemv_w4a16_stream_kernel<2>, d_items,
+                                            d_tiles, d_begin, b->m, xo, yo, pl.stages, pl.x_buf_halfs, pl.xs_buf_floats,
+                                            pl.x_raw_bytes, pl.x_raw_depth, pl.x_bufs, b->item_done, counted, b->status);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "gemv_w4a16_stream_kernel launch");
+  Q35B_CUDA_TRY(le, "gemv_w4a16_stream_kernel launch");
   return Q35B_OK;
 }
 

@@ -53,6 +53,25 @@ def _time_graphs(torch, stream, graphs, reps: int) -> float:
     return statistics.median(times)
 
 
+def _time_launches(torch, stream, fns, reps: int) -> float:
+    """Median microseconds per call, cycling through `fns` as back-to-back launches on `stream` (the work-list kernel
+    is launched with programmatic stream serialisation, so consecutive launches overlap head and tail)."""
+    with torch.cuda.stream(stream):
+        for i in range(max(3, len(fns))):
+            fns[i % len(fns)]()
+        stream.synchronize()
+        times = []
+        for block in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(reps):
+                fns[(block * reps + i) % len(fns)]()
+            e1.record(stream)
+            stream.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / reps)
+    return statistics.median(times)
+
+
 def _capture(torch, stream, fn):
     with torch.cuda.stream(stream):
         fn()
@@ -83,9 +102,9 @@ def decode_entries(q, torch, device, peaks, shapes, layers, ms, label, row_outli
         xs = [torch.randn((m, k), generator=gen, device=device).to(torch.bfloat16) for _ in range(layers) for _, k in shapes]
         ys = [torch.empty((m, n), dtype=torch.bfloat16, device=device) for _ in range(layers) for n, _ in shapes]
         kernel = "gemv_w4a16_stream_kernel (work list)"
+        graphs = None
         try:
             batches = [q.GemvBatch(list(zip(ws, xs, ys)), m) for ws in weights]
-            graphs = [_capture(torch, stream, b.run) for b in batches]
         except q.Q35bError as e:
             # activations too large for the streaming kernel's shared memory: per-projection SIMT launches
             kernel = f"gemv_w4a16_simt_kernel per projection ({e})"
@@ -96,7 +115,10 @@ def decode_entries(q, torch, device, peaks, shapes, layers, ms, label, row_outli
                     q.gemv_w4a16(w, x, out=y, kernel=q.GEMV_SIMT)
 
             graphs = [_capture(torch, stream, lambda ws=ws: run_set(ws)) for ws in weights]
-        us = _time_graphs(torch, stream, graphs, reps=10)
+        if graphs is None:
+            us = _time_launches(torch, stream, [b.run for b in batches], reps=20)
+        else:
+            us = _time_graphs(torch, stream, graphs, reps=10)
         nbytes = layers * sum(_alg_bytes(n, k, m) for n, k in shapes)
         gbs = nbytes / us / 1e3
         for b in batches:
