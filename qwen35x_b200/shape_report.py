@@ -283,7 +283,8 @@ def to_markdown(report: dict) -> str:
     """The report as the tables kept under profiles/ (written next to the JSON by `bench.py --report`)."""
     pk = report["peaks"]
     out = ["# Per-shape throughput report (1 x B200)", "",
-           "Command: `python bench.py --report <path>.json` (CUDA-graph replays, CUDA events on the launching stream, "
+           "Command: `python bench.py --report <path>.json` (decode work lists as back-to-back launches, everything else "
+           "as CUDA-graph replays; CUDA events on the launching stream, "
            "median of 5 blocks; weights/operands rotated through more than L2-size worth of copies; synthetic seeded "
            f"tensors quantised on the GPU). Peaks: measured HBM copy {pk['hbm_gbs']:.0f} GB/s; FP4 tensor: nominal "
            f"{FP4_NOMINAL_TFLOPS:.0f} TFLOP/s dense (no measured FP4 peak exists; 4 x measured BF16 burst = "
