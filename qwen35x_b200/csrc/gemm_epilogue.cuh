@@ -111,6 +111,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int row, int col0, int n, float g,
                                                    const GemmEpilogue & ep, __nv_bfloat16 * __restrict__ c, int ldc,
                                                    bool to_peers = true) {
+  if (col0 >= n) return;  // a chunk wholly past the last column of a partial tile
   const int n_peers = to_peers ? ep.n_peers : 0;
   const float alpha = g * ep.s2;
   if (ep.gate_up) {
