@@ -57,9 +57,13 @@ amax_to_global_scale_kernel(const T * __restrict__ x, size_t n, unsigned int * _
   if constexpr (sizeof(T) == 2) {
     const uint4 * v = reinterpret_cast<const uint4 *>(x);
     const size_t nv = n >> 3;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv; i += stride) {
-      local = fmaxf(local, abs_max8(__ldg(v + i)));
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    // four independent 16-byte loads in flight per thread
+    for (; i + 3 * stride < nv; i += 4 * stride) {
+      const uint4 a = __ldg(v + i), b = __ldg(v + i + stride), c = __ldg(v + i + 2 * stride), d = __ldg(v + i + 3 * stride);
+      local = fmaxf(fmaxf(local, fmaxf(abs_max8(a), abs_max8(b))), fmaxf(abs_max8(c), abs_max8(d)));
     }
+    for (; i < nv; i += stride) local = fmaxf(local, abs_max8(__ldg(v + i)));
   } else {
     const float4 * v = reinterpret_cast<const float4 *>(x);
     const size_t nv = n >> 2;
@@ -202,8 +206,9 @@ int check_quant_args(const void * x, int m, int k, const void * codes, const voi
 
 template <typename T>
 int launch_amax(const T * x, size_t n, unsigned int * ws, float * g_out, cudaStream_t s) {
+  // few blocks (every one ends with two atomics on the same pair of words), each with plenty of loads in flight
   const size_t per_block = static_cast<size_t>(kThreads) * 8 * 4;
-  int blocks = static_cast<int>(std::min<size_t>((n + per_block - 1) / per_block, static_cast<size_t>(sm_count()) * 8));
+  int blocks = static_cast<int>(std::min<size_t>((n + per_block - 1) / per_block, static_cast<size_t>(sm_count()) * 4));
   if (blocks < 1) blocks = 1;
   amax_to_global_scale_kernel<T><<<blocks, kThreads, 0, s>>>(x, n, ws, g_out);
   count_launch();

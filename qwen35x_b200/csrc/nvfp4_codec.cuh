@@ -111,9 +111,17 @@ Q35B_HD uint8_t encode_e2m1_scan(float value) {
 // fp32 -> E2M1 nibble, nearest magnitude with ties to the smaller one, sign
 // bit = (value < 0) (src/runtime/cuda_bench.cu:926-940).
 // The same for |value| < 2^20 or NaN (the scan also gives 0 for NaN): no range check, no branch.
+// From 1.0 up the levels are 2^e and 1.5 * 2^e, i.e. the magnitude rounded to one mantissa bit with ties going down:
+// adding just under half a step to the bit pattern and dropping 22 bits counts half-exponent steps above 1.0
+// (a mantissa carry moves on to the next exponent by itself); level index = 2 + steps, at most 7.  Below 1.0 the
+// levels 0, 0.5, 1.0 are told apart by two comparisons.
 Q35B_HD uint8_t encode_e2m1_bounded(float value) {
-  const float a = bits_f32(f32_bits(value) & 0x7fffffffu);
-  const unsigned code = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+  const uint32_t au = f32_bits(value) & 0x7fffffffu;
+  const float a = bits_f32(au);
+  const unsigned steps = (au + 0x1fffffu - 0x3f800000u) >> 22;
+  const unsigned high = steps + 2u < 7u ? steps + 2u : 7u;
+  const unsigned low = (a > 0.25f) + (a > 0.75f);
+  const unsigned code = (a >= 1.0f) ? high : low;  // NaN takes the low branch and gets 0, like the scan
   return static_cast<uint8_t>(((value < 0.0f) ? 8u : 0u) | code);
 }
 

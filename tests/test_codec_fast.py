@@ -58,6 +58,13 @@ def test_e2m1_switch_points(oracle, engine):
             for sign in (0, 0x80000000):
                 v = _f((b + d) | sign)
                 assert E.q35b_debug_encode_e2m1(v) == L.q35o_encode_e2m1(v), hex(b + d)
+    assert _switch_points(lambda v: E.q35b_debug_encode_e2m1(v), lo, hi) == pts
+    # every exponent of the encoder's range at a spread of mantissas, both signs
+    for e in range(0, 147):
+        for mant in (0, 1, 0x1FFFFF, 0x200000, 0x200001, 0x3FFFFF, 0x400000, 0x5FFFFF, 0x600000, 0x600001, 0x7FFFFF):
+            for sign in (0, 0x80000000):
+                v = _f((e << 23) | mant | sign)
+                assert E.q35b_debug_encode_e2m1(v) == L.q35o_encode_e2m1(v), hex((e << 23) | mant)
     rng = np.random.default_rng(6)
     vals = list((rng.standard_normal(20000) * 4).astype(np.float32))
     vals += [0.0, -0.0, float("nan"), float("inf"), -float("inf"), 2.0 ** 20, -(2.0 ** 27), 1e30, -3e38]
