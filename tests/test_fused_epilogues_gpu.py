@@ -270,6 +270,35 @@ def test_work_list_with_dependencies(engine, oracle, m):
         assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(y)), oracle.bf16_to_f32(y_bits)) <= 2 * REL_L2_TOL
 
 
+def test_work_list_dependency_without_activation_ring(engine, oracle):
+    """4B-class MLP block at M = 8: the down projection's activations (8 x 9216) leave no room for the raw-activation
+    ring, so the activation warp reads the gate/up output straight from global memory once it is complete."""
+    import torch
+
+    m, hidden, inter = 8, 2560, 9216
+    _, g_codes, g_scales, g_s2 = make_weight(inter, hidden, seed=81, std=0.05)
+    _, u_codes, u_scales, u_s2 = make_weight(inter, hidden, seed=82, std=0.03)
+    _, d_codes, d_scales, d_s2 = make_weight(hidden, inter, seed=83, std=0.05)
+    xb = make_activations(m, hidden, seed=84)
+    gu = engine.Nvfp4Weight.gate_up_from_host(g_codes, g_scales, g_s2, u_codes, u_scales, u_s2)
+    down = engine.Nvfp4Weight.from_host(d_codes, d_scales, d_s2)
+    x = to_torch_bf16(xb)
+    h = torch.zeros((m, inter), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((m, hidden), dtype=torch.bfloat16, device="cuda")
+    batch = engine.GemvBatch([(gu, x, h), (down, h, y, x, 0)], m)
+    for _ in range(2):
+        batch.run()
+    torch.cuda.synchronize()
+    assert batch.status() == 0
+    _, gate = oracle.gemv_bf16(g_codes, g_scales, g_s2, xb, threads=8)
+    _, up = oracle.gemv_bf16(u_codes, u_scales, u_s2, xb, threads=8)
+    h_bits = oracle.bf16_round((gate / (np.float32(1.0) + np.exp(-gate, dtype=np.float32)) * up).astype(np.float32))
+    _, d = oracle.gemv_bf16(d_codes, d_scales, d_s2, h_bits, threads=8)
+    y_bits = oracle.bf16_round(d + oracle.bf16_to_f32(xb))
+    assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(h)), oracle.bf16_to_f32(h_bits)) <= 2 * REL_L2_TOL
+    assert oracle.rel_l2(oracle.bf16_to_f32(from_torch_bf16(y)), oracle.bf16_to_f32(y_bits)) <= 2 * REL_L2_TOL
+
+
 def test_work_list_dependency_must_point_backwards(engine):
     import torch
 
