@@ -7,7 +7,7 @@ microseconds, GB/s of algorithmic bytes (decode) or TFLOP/s (prefill), and the f
 roofline.  Inputs are seeded synthetic tensors quantised on the GPU; weights are rotated through enough copies that
 no launch finds its operands in L2.
 
-    python bench.py --report gpurun_out/shape_report.json
+    python bench.py --report shape_report.json
 """
 from __future__ import annotations
 
