@@ -335,7 +335,20 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
     widest = max(c for _, c in sharding.shard_layout(n, world))
     gathered = torch.empty((world * m, widest), dtype=torch.bfloat16, device=device) if world > 1 else None
     # the gather fused into the GEMM's stores: every rank owns a full [m, n] matrix the other ranks store into
-    peer = sharding.PeerGather(m, n) if world > 1 else None
+    peer, peer_error = None, None
+    if world > 1:
+        # every rank must reach the same decision, so the outcome of the set-up is agreed on before it is used
+        try:
+            peer = sharding.PeerGather(m, n)
+            ok = 1
+        except Exception as e:  # noqa: BLE001 - reported in the JSON line, the NCCL exchange is timed instead
+            peer_error = f"{type(e).__name__}: {e}"
+            ok = 0
+        flag = torch.tensor([ok], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            peer = None
+            peer_error = peer_error or "set-up failed on another rank"
     counter = [0]
 
     def one(with_quant: bool, with_gather: bool, index=None, fused: bool = True):
@@ -345,7 +358,7 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
             a_codes, a_scales, g = q.quantize_activations(x, scratch=scratch)
         else:
             a_codes, a_scales, g = scratch[0].view(m, k // 2), scratch[1], scratch[2]
-        if world > 1 and with_gather and fused:
+        if peer is not None and with_gather and fused:
             peer.project(weight, a_codes, a_scales, g)  # GEMM storing into every rank's [m, n] + bounded wait
             return
         q.gemm_w4a4(weight, a_codes, a_scales, g, m, out=out)
@@ -404,7 +417,8 @@ def bench_gemm(args, q, torch, dist, device, rank, world, pk, timed_barrier) -> 
         "gemm_only": {"ms": round(ms_gemm, 4), "tflops": round(tf, 1)},
         "quant_gemm_gather": {"ms": round(ms_full, 4), "tflops": round(flops / (ms_full * 1e-3) / 1e12, 1),
                               "exchange": "none (1 GPU)" if world == 1 else
-                              "GEMM epilogue stores into every rank's [M, N] over NVLink (peer memory) + flag wait"},
+                              ("GEMM epilogue stores into every rank's [M, N] over NVLink (peer memory) + flag wait"
+                               if peer is not None else f"NCCL all-gather (peer buffers unavailable: {peer_error})")},
         **({"quant_gemm_nccl_gather": {"ms": round(ms_nccl, 4), "tflops": round(flops / (ms_nccl * 1e-3) / 1e12, 1),
                                        "exchange": "NCCL all-gather of the BF16 slabs after the GEMM"}} if world > 1 else {}),
         "roofline": {"bound": "tensor", "achieved": round(tf / world, 1), "peak": fp4_peak_nominal, "unit": "TFLOP/s",

@@ -89,14 +89,34 @@ class PeerGather:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.m, self.n = m, n
-        self.local = engine.PeerBuffer.create(m, n)
-        mine = torch.frombuffer(bytearray(self.local.export()), dtype=torch.uint8).cuda()
-        handles = torch.empty((self.world, mine.numel()), dtype=torch.uint8, device=mine.device)
+        device = torch.device("cuda", torch.cuda.current_device())
+
+        def agree(error):
+            """Every rank learns whether any rank failed the last local step, so that all raise or none does."""
+            flag = torch.tensor([0 if error is None else 1], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+            if int(flag.item()) != 0:
+                raise RuntimeError(f"peer buffer set-up failed: {error if error is not None else 'on another rank'}")
+
+        error, self.local = None, None
+        nbytes = int(engine.lib().q35b_peer_buffer_handle_bytes())
+        try:
+            self.local = engine.PeerBuffer.create(m, n)
+            mine = torch.frombuffer(bytearray(self.local.export()), dtype=torch.uint8).to(device)
+        except Exception as e:  # noqa: BLE001 - turned into one error on every rank
+            error = e
+            mine = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        agree(error)
+        handles = torch.empty((self.world, nbytes), dtype=torch.uint8, device=device)
         dist.all_gather_into_tensor(handles, mine, group=group)
         handles = handles.cpu().numpy()
-        self.buffers = [self.local if r == self.rank else engine.PeerBuffer.open(handles[r].tobytes(), m, n)
-                        for r in range(self.world)]
-        self.status = torch.zeros(1, dtype=torch.int32, device=mine.device)
+        try:
+            self.buffers = [self.local if r == self.rank else engine.PeerBuffer.open(handles[r].tobytes(), m, n)
+                            for r in range(self.world)]
+        except Exception as e:  # noqa: BLE001
+            error = e
+        agree(error)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.epoch = 0
         dist.barrier(group)
 
