@@ -104,6 +104,11 @@ __global__ void __launch_bounds__(kThreads)
 gemv_w4a16_simt_kernel(const uint8_t * __restrict__ codes, const uint8_t * __restrict__ scales,
                        const XT * __restrict__ x, OT * __restrict__ y, int rows, int k, float s2_scaled,
                        float x_scale) {
+  // Launched with programmatic stream serialisation: the grid may be scheduled while the previous kernel of the
+  // stream drains (a 2 MB projection is shorter than a launch), but reads and writes nothing before that kernel is
+  // complete and visible.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int row0 = warp * RW;
@@ -214,10 +219,21 @@ int launch_simt(const q35b_weight * w, const XT * x, OT * y, float x_scale, cuda
   constexpr int RW = (M <= 2) ? 2 : 1;
   const int warps = (w->rows + RW - 1) / RW;
   const int blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  gemv_w4a16_simt_kernel<M, RW, XT, OT><<<blocks, kThreads, 0, s>>>(w->codes, w->scales, x, y, w->rows, w->k,
-                                                                   w->s2 * 16384.0f, x_scale);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const uint8_t * codes = w->codes;
+  const uint8_t * scales = w->scales;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_w4a16_simt_kernel<M, RW, XT, OT>, codes, scales, x, y, w->rows, w->k,
+                                            w->s2 * 16384.0f, x_scale);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "gemv_w4a16_simt_kernel launch");
+  Q35B_CUDA_TRY(le, "gemv_w4a16_simt_kernel launch");
   return Q35B_OK;
 }
 
