@@ -152,6 +152,9 @@ typedef struct q35b_gemv_item {
   int after;                  /* 0: independent; k > 0: runs after item k - 1 of the same list (k - 1 < own index) */
 } q35b_gemv_item;
 
+/* sizeof(q35b_gemv_item) as this library was built: lets a foreign-function binding check its own struct layout. */
+Q35B_API size_t q35b_gemv_item_bytes(void);
+
 typedef struct q35b_gemv_batch q35b_gemv_batch;
 /* Builds the tile schedule and uploads the descriptors (allocates, synchronises). */
 Q35B_API int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out);

@@ -287,6 +287,8 @@ int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void
   return launch_gemv_bf16(w, x_bf16, m, y_bf16, kernel, static_cast<cudaStream_t>(stream));
 }
 
+size_t q35b_gemv_item_bytes(void) { return sizeof(q35b_gemv_item); }
+
 int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out) {
   return gemv_batch_build(items, count, m, out);
 }

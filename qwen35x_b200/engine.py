@@ -86,6 +86,10 @@ def lib() -> C.CDLL:
     L.q35b_project_prefill_bf16_static.argtypes = [vp, vp, i, f, vp, i, vp]
     L.q35b_gemm_w4a4_bf16_residual.restype = i
     L.q35b_gemm_w4a4_bf16_residual.argtypes = [vp, vp, vp, vp, i, vp, i, vp, i, vp, vp]
+    L.q35b_gemv_item_bytes.restype = C.c_size_t
+    L.q35b_gemv_item_bytes.argtypes = []
+    if int(L.q35b_gemv_item_bytes()) != C.sizeof(_GemvItem):
+        raise Q35bError(1, "q35b_gemv_item layout of this binding does not match the library.")
     L.q35b_peer_buffer_create.restype = i
     L.q35b_peer_buffer_create.argtypes = [C.c_size_t, C.POINTER(vp)]
     L.q35b_peer_buffer_handle_bytes.restype = C.c_size_t
