@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 REL_L2_TOL = 1e-3
 
 
-@pytest.mark.parametrize("world,m,n,k", [(2, 300, 1024, 512), (3, 64, 1152, 256), (4, 257, 2560, 512)])
+@pytest.mark.parametrize("world,m,n,k", [(2, 300, 1024, 512), (3, 64, 1152, 256), (4, 257, 2560, 512), (8, 130, 2048, 256),
+                                         (8, 300, 3584, 512)])
 def test_emulated_ranks_fill_every_matrix(engine, oracle, world, m, n, k):
     import torch
 
