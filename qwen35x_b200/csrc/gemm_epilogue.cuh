@@ -46,27 +46,49 @@ struct GemmEpilogue {
   unsigned int epoch = 0;
 };
 
+__device__ __forceinline__ void st_global_v8(void * p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
 // A warp that has just stored 32 rows x COLS BF16 columns of the local matrix (one row per lane) sends them to the
-// other ranks as whole lines: it reads its rows back from L2 with eight lanes per 128 bytes and repeats them with the
+// other ranks as whole lines: it reads its rows back from L2 with four lanes per 128 bytes and repeats them with the
 // same lane mapping, so every store instruction covers whole 128-byte lines of a few rows, the unit NVLink moves
-// well, instead of thirty-two 32-byte pieces of thirty-two rows.  col0 and n are multiples of 8 (row shards are
+// well, instead of thirty-two 32-byte pieces of thirty-two rows.  col0 and n are multiples of 16 (row shards are
 // cut on 128-row boundaries); pieces past column n or row m are skipped.
 template <int COLS>
 __device__ __forceinline__ void gemm_forward_rows_to_peers(const GemmEpilogue & ep, const __nv_bfloat16 * c, int ldc,
                                                            int row0, int m, int col0, int n, int lane) {
-  constexpr int kPieces = COLS / 8;  // 16-byte pieces per row
-  __threadfence_block();             // the lanes' own stores, before other lanes read them
+  constexpr int kPieces = COLS / 16;  // 32-byte pieces per row
+  __threadfence_block();              // the lanes' own stores, before other lanes read them
   __syncwarp();
+  // all loads first, then all stores: a warp issues in order, so a store waiting for its load would hold back the
+  // loads behind it
+  uint32_t v[kPieces][8];
 #pragma unroll
   for (int it = 0; it < kPieces; ++it) {
     const int idx = it * 32 + lane;
     const int row = row0 + idx / kPieces;
-    const int col = col0 + (idx % kPieces) * 8;
-    if (row < m && col + 8 <= n) {
+    const int col = col0 + (idx % kPieces) * 16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[it][j] = 0u;
+    if (row < m && col + 16 <= n) {
+      const __nv_bfloat16 * src = c + static_cast<size_t>(row) * ldc + col;
+      asm volatile("ld.global.cg.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=r"(v[it][0]), "=r"(v[it][1]), "=r"(v[it][2]), "=r"(v[it][3]), "=r"(v[it][4]), "=r"(v[it][5]),
+                     "=r"(v[it][6]), "=r"(v[it][7])
+                   : "l"(src));
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < kPieces; ++it) {
+    const int idx = it * 32 + lane;
+    const int row = row0 + idx / kPieces;
+    const int col = col0 + (idx % kPieces) * 16;
+    if (row < m && col + 16 <= n) {
       const size_t off = static_cast<size_t>(row) * ldc + col;
-      uint4 v;
-      asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(c + off));
-      _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < ep.n_peers) *reinterpret_cast<uint4 *>(ep.peer_c[i] + off) = v;
+      _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < ep.n_peers) st_global_v8(ep.peer_c[i] + off, v[it]);
     }
   }
 }
@@ -90,11 +112,6 @@ __device__ __forceinline__ void gemm_signal_peers(const GemmEpilogue & ep, bool 
   }
 }
 
-__device__ __forceinline__ void st_global_v8(void * p, const uint32_t (&v)[8]) {
-  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
-               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
-               : "memory");
-}
 
 // silu(g) * u with the hardware exponential and reciprocal (a few fp32 ulp, far inside the BF16 rounding that follows)
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
