@@ -47,7 +47,7 @@ __device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g
     d = fmaxf(__fdiv_rn(amax, 6.0f), 1.0e-8f);
     sb = encode_ue4m3(d);
   }
-  uint32_t word[2] = {0u, 0u};
+  uint32_t code[16];
   // exponents of d and amax inside [2^-60, 2^60]: no intermediate of div_by_shared can overflow, and a quotient
   // small enough to lose bits is far below the first rounding boundary (0.25); amax < 2^19 d keeps every quotient
   // inside the range of the branch-free encoder
@@ -57,18 +57,20 @@ __device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
     r = __fmaf_rn(r, __fmaf_rn(-d, r, 1.0f), r);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t c = encode_e2m1_bounded(div_by_shared(v[i], d, r));
-      const int nib = swap ? (i ^ 1) : i;
-      word[nib >> 3] |= c << ((nib & 7) * 4);
-    }
+    for (int i = 0; i < 16; ++i) code[i] = encode_e2m1_bounded(div_by_shared(v[i], d, r));
   } else {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t c = encode_e2m1(__fdiv_rn(v[i], d));
-      const int nib = swap ? (i ^ 1) : i;
-      word[nib >> 3] |= c << ((nib & 7) * 4);
-    }
+    for (int i = 0; i < 16; ++i) code[i] = encode_e2m1(__fdiv_rn(v[i], d));
+  }
+  // element 2j in the low nibble of byte j: eight codes per word, built as word * 16 + code from the top down
+  // (multiply-adds, which leave the comparison pipe to the encoders); the reference's cuBLASLt order swaps the two
+  // nibbles of every byte afterwards
+  uint32_t word[2] = {0u, 0u};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int i = 7; i >= 0; --i) word[h] = word[h] * 16u + code[8 * h + i];
+    if (swap) word[h] = ((word[h] & 0x0f0f0f0fu) << 4) | ((word[h] >> 4) & 0x0f0f0f0fu);
   }
   out = make_uint2(word[0], word[1]);
   return sb;
