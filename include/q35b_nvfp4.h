@@ -158,7 +158,11 @@ Q35B_API size_t q35b_gemv_item_bytes(void);
 typedef struct q35b_gemv_batch q35b_gemv_batch;
 /* Builds the tile schedule and uploads the descriptors (allocates, synchronises). */
 Q35B_API int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out);
-/* One kernel launch on `stream`; no allocation, no synchronisation. */
+/* One kernel launch on `stream`; no allocation, no synchronisation.  The launch uses programmatic stream
+ * serialisation: the kernel may begin streaming WEIGHTS while the previous kernel of the stream is still finishing
+ * (activations, residuals and outputs are touched only after that kernel is complete).  Weights are therefore
+ * treated as constant from q35b_weight_create* on; a host that rewrites weight memory must synchronise the stream
+ * before the next run. */
 Q35B_API int q35b_gemv_batch_run(const q35b_gemv_batch * batch, q35b_stream stream);
 Q35B_API void q35b_gemv_batch_destroy(q35b_gemv_batch * batch);
 /* Copies the batch's device status word to the host (synchronises): 0, or the code of a bounded device-side wait
