@@ -30,6 +30,15 @@ __device__ __forceinline__ float div_by_shared(float x, float d, float r) {
   return __fmaf_rn(e, r, q);
 }
 
+// encode_e2m1_bounded (nvfp4_codec.cuh) on 32-bit values throughout: no narrowing to a byte and back per element.
+__device__ __forceinline__ uint32_t e2m1_code_bounded(float q) {
+  const uint32_t au = __float_as_uint(q) & 0x7fffffffu;
+  const float a = __uint_as_float(au);
+  const uint32_t high = min((au + (0x1fffffu - 0x3f800000u + 0x800000u)) >> 22, 7u);  // 2 + half-exponent steps above 1.0
+  const uint32_t low = (a > 0.25f ? 1u : 0u) + (a > 0.75f ? 1u : 0u);
+  return ((a >= 1.0f) ? high : low) | ((q < 0.0f) ? 8u : 0u);
+}
+
 // Quantise one 16-block; returns the scale byte, writes 8 code bytes.
 template <int RECIPE>
 __device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g, bool swap, uint2 & out) {
@@ -57,7 +66,7 @@ __device__ __forceinline__ uint32_t quantize_block(const float (&v)[16], float g
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
     r = __fmaf_rn(r, __fmaf_rn(-d, r, 1.0f), r);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) code[i] = encode_e2m1_bounded(div_by_shared(v[i], d, r));
+    for (int i = 0; i < 16; ++i) code[i] = e2m1_code_bounded(div_by_shared(v[i], d, r));
   } else {
 #pragma unroll
     for (int i = 0; i < 16; ++i) code[i] = encode_e2m1(__fdiv_rn(v[i], d));
