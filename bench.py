@@ -132,11 +132,11 @@ def build_decode_model(q, torch, device, seed: int, sets: int):
     return models
 
 
-def decode_buffers(torch, device, seed: int):
-    """Host (pinned) and device activations / outputs for one step, packed back to back."""
+def decode_buffers(torch, device, seed: int, m: int = 1):
+    """Host (pinned) and device activations / outputs for one step of `m` tokens, packed back to back."""
     shapes = [s for _ in range(LAYERS_0P8B) for s in SHAPES_0P8B]
-    x_elems = sum(k for _, k in shapes)
-    y_elems = sum(n for n, _ in shapes)
+    x_elems = m * sum(k for _, k in shapes)
+    y_elems = m * sum(n for n, _ in shapes)
     gen = torch.Generator().manual_seed(seed)
     x_host = torch.randn(x_elems, generator=gen, dtype=torch.float32).to(torch.bfloat16).pin_memory()
     y_host = torch.empty(y_elems, dtype=torch.bfloat16).pin_memory()
@@ -144,10 +144,10 @@ def decode_buffers(torch, device, seed: int):
     y_dev = torch.zeros(y_elems, dtype=torch.bfloat16, device=device)
     xs, ys, xo, yo = [], [], 0, 0
     for n, k in shapes:
-        xs.append(x_dev[xo:xo + k].view(1, k))
-        ys.append(y_dev[yo:yo + n].view(1, n))
-        xo += k
-        yo += n
+        xs.append(x_dev[xo:xo + m * k].view(m, k))
+        ys.append(y_dev[yo:yo + m * n].view(m, n))
+        xo += m * k
+        yo += m * n
     return shapes, x_host, y_host, x_dev, y_dev, xs, ys
 
 
@@ -164,13 +164,13 @@ def run_engine(args, rank: int, world: int, local_rank: int) -> dict | None:
     pk = peaks()
     sets = 2
     models = build_decode_model(q, torch, device, seed=42 + rank, sets=sets)
-    shapes, x_host, y_host, x_dev, y_dev, xs, ys = decode_buffers(torch, device, seed=7 + rank)
-    step_bytes = sum(algorithmic_bytes(n, k, 1) for n, k in shapes)
+    shapes, x_host, y_host, x_dev, y_dev, xs, ys = decode_buffers(torch, device, seed=7 + rank, m=args.m)
+    step_bytes = sum(algorithmic_bytes(n, k, args.m) for n, k in shapes)
     launches_per_step = len(shapes)
     stream = torch.cuda.Stream(device=device)
 
     # The step's work list: all 96 projections in one persistent launch (they are independent in this workload).
-    batches = [q.GemvBatch(list(zip(models[s], xs, ys)), 1) for s in range(sets)]
+    batches = [q.GemvBatch(list(zip(models[s], xs, ys)), args.m) for s in range(sets)]
 
     def step(set_index: int):
         batches[set_index].run()
@@ -311,7 +311,7 @@ def run_engine(args, rank: int, world: int, local_rank: int) -> dict | None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 weights x bf16 activations, fp32 accumulate",
         "data": "synthetic",
-        "config": {"workload": "0.8B-class decode step, M=1, 24 layers x {[4096,1024],[1024,2048],[7168,1024],"
+        "config": {"workload": f"0.8B-class decode step, M={args.m}, " "24 layers x {[4096,1024],[1024,2048],[7168,1024],"
                                "[1024,3584]} NVFP4 projections (BASELINE configs[1])",
                    "bytes_per_step": step_bytes, "launch": "one persistent work-list launch over the step's 96 projections per step, back to back on one "
                                                           "stream with programmatic dependent launch (issued from CUDA "
@@ -329,7 +329,7 @@ def run_engine(args, rank: int, world: int, local_rank: int) -> dict | None:
                      "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
                                        "profiles/gemv_w4a16_stream_decode_step_0p8b.md",
                      "peak_source": pk["source"],
-                     "kernel": "gemv_w4a16_stream_kernel (M=1)", "bytes_per_launch": step_bytes // launches_per_step},
+                     "kernel": f"gemv_w4a16_stream_kernel (M={args.m})", "bytes_per_launch": step_bytes // launches_per_step},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 5)},
         "gpu_launches": launches_per_step * args.steps,
@@ -602,6 +602,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["engine", "reference"], default="engine")
+    ap.add_argument("--m", type=int, default=1, choices=range(1, 9), metavar="TOKENS",
+                    help="tokens per decode step (1..8); the headline and the driver's runs use 1")
     ap.add_argument("--report", default="", help="write the per-shape throughput report (JSON) to this path and exit")
     ap.add_argument("--only", choices=["all", "decode", "gemm"], default="all",
                     help="profiling aid: 'decode' skips the GEMM, the per-projection-launch figure and the CPU "

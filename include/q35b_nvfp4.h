@@ -18,6 +18,16 @@
  *   - All device pointers belong to the caller except the repacked weight,
  *     which the engine owns.  No call below allocates or synchronises unless
  *     it says so; every launch goes to the given stream.
+ *   - A weight belongs to the device that was current when it was created;
+ *     calls that take it must be made with that device current
+ *     (Q35B_ERR_ARGUMENT otherwise).
+ *   - Threads: a weight is immutable after q35b_weight_create* (its tensor
+ *     maps are encoded there), so any number of host threads may project
+ *     through the same weight at once, each on its own stream; the one piece
+ *     of state built later (the single-projection work list of
+ *     Q35B_GEMV_STREAM, per token count) is created under a lock.  A
+ *     q35b_gemv_batch, a q35b_peer_buffer and the built-in scratch of
+ *     q35b_project_prefill_bf16_static serve one call at a time.
  *   - There is no CPU fallback: without a CUDA device every compute entry
  *     point fails with Q35B_ERR_CUDA.
  */
@@ -77,9 +87,11 @@ Q35B_API unsigned long long q35b_launch_count(void);
  * device.  Replaces load_modelopt_nvfp4_state's per-module repack
  * (src/runtime/qwen35x_cuda_backend.cpp:1582-1695: pad_nvfp4_weight_for_tensor_core :967,
  * swizzle_nvfp4_block_scale_for_tensor_core :990, pack_nvfp4_weight_for_sm120_mma :1029).
- * Keeps rows [shard_index * ceil128(N / shard_count) ...) of the tensor: the
- * shard boundaries are multiples of 128 rows except for the last shard.
- * Allocates device memory and synchronises the legacy default stream. */
+ * Keeps the rows q35b_shard_range(n, shard_index, shard_count) names: the tensor's 128-row blocks (the height of
+ * a scale tile) are dealt out as evenly as possible, shard i taking blocks [B*i/count, B*(i+1)/count) of
+ * B = ceil(n/128), so every shard starts on a multiple of 128 rows and shards differ by at most one block
+ * (n = 2560 over 8 shards: 384, 256, 384, 256, ...).
+ * Allocates device memory, encodes the weight's tensor maps and synchronises the legacy default stream. */
 Q35B_API int q35b_weight_create(const uint8_t * codes_host, const uint8_t * scales_host, float weight_scale_2,
                                 float input_scale, int n, int k, int shard_index, int shard_count,
                                 q35b_weight ** out);
@@ -192,6 +204,13 @@ Q35B_API int q35b_quantize_nvfp4_bf16(const void * x_bf16, int m, int k, float g
                                       uint8_t * scales_tiled, float * input_scale_dev, void * workspace,
                                       q35b_stream stream);
 
+/* Same from fp32 activations [m, k], the input type of the reference's prefill benchmark
+ * (nvfp4_quantize_matrix_for_cublaslt_kernel, src/runtime/cuda_bench.cu:141-176, fed by
+ * src/runtime/runtime.cpp:498-501).  x_f32 16-byte aligned. */
+Q35B_API int q35b_quantize_nvfp4_f32(const float * x_f32, int m, int k, float global_scale, uint8_t * codes,
+                                     uint8_t * scales_tiled, float * input_scale_dev, void * workspace,
+                                     q35b_stream stream);
+
 /* The reference's own activation recipe (no per-tensor scale, divisor =
  * unrounded block scale, src/runtime/cuda_bench.cu:178-213), kept so the
  * quantiser can be checked byte-for-byte against the reference's kernel.
@@ -205,10 +224,17 @@ Q35B_API int q35b_quantize_nvfp4_bf16_reference_recipe(const void * x_bf16, int 
  * run_nvfp4_cublaslt_prefill_projection_device (src/runtime/cuda_bench.cu:1056-1167)
  * and the fp32->bf16 pass after it (src/kernels/cuda/prefill.cu:639).
  * Requires k % 64 == 0.  status_dev: 4 bytes of device memory, zero on entry,
- * nonzero afterwards if a bounded device-side wait expired (may be NULL). */
+ * nonzero afterwards if a bounded device-side wait expired.  With status_dev
+ * NULL the call uses a word inside the library (one per device, cleared on the
+ * stream ahead of the launch, nothing allocated); q35b_gemm_default_status
+ * reads it.  Calls that share that word and overlap on the GPU can clear each
+ * other's code: pass an own word where that matters. */
 Q35B_API int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
                                  const float * input_scale_dev, int m, void * c_bf16, int ldc,
                                  unsigned int * status_dev, q35b_stream stream);
+
+/* Copies the library's status word of the current device to the host (synchronises the device). */
+Q35B_API int q35b_gemm_default_status(unsigned int * status_out);
 
 /* Same GEMM with the residual add fused into the epilogue: c = bf16(projection + residual), residual [m, rows] BF16
  * with row stride ldr.  Replaces pf_add_residual_bf16 after the down / o projections
@@ -242,7 +268,10 @@ Q35B_API int q35b_gemm_w4a4_gate_up_nvfp4(const q35b_weight * w, const uint8_t *
  * Use a new, larger epoch per gathered matrix.  One process per GPU: create the local buffer, pass its handle
  * (q35b_peer_buffer_handle_bytes() bytes) to the other ranks by any host channel, open theirs.  buffers[world] lists
  * the mappings by rank, buffers[rank] being the local one.  In one process (tests, several GPUs under one host
- * thread) created buffers can be listed directly. */
+ * thread) created buffers can be listed directly.
+ * Any ldc >= the full width works; when ldc, the shard's column count and the matrices' bases are multiples of 16
+ * elements (true for every 128-row shard cut of a contiguous [m, N] matrix) the remote stores are whole 128-byte
+ * lines, otherwise each lane repeats its own 32-byte (or scalar) stores. */
 typedef struct q35b_peer_buffer q35b_peer_buffer;
 Q35B_API int q35b_peer_buffer_create(size_t data_bytes, q35b_peer_buffer ** out);
 Q35B_API size_t q35b_peer_buffer_handle_bytes(void);
@@ -274,8 +303,12 @@ Q35B_API int q35b_peer_gather_wait(q35b_peer_buffer * const * buffers, int world
  *    first call outside any stream capture.
  *  - All calls on a device share the one scratch area: two calls that may overlap on the GPU (different streams
  *    without an ordering between them, or different threads) race on it.  Serialise them.
- *  - The area keeps the previous call's bytes; the words that must start at zero are cleared by every call. */
+ *  - The area keeps the previous call's bytes; the words that must start at zero are cleared by every call.
+ *  - A bounded device-side wait that expired leaves its code in the scratch's status word until the next call
+ *    clears it: q35b_static_prefill_status copies that word of the current device to the host (it synchronises
+ *    the device, so it also waits for the call it reports on). */
 Q35B_API size_t q35b_static_prefill_capacity_bytes(void);
+Q35B_API int q35b_static_prefill_status(unsigned int * status_out);
 Q35B_API int q35b_project_prefill_bf16_static(const q35b_weight * w, const void * x_bf16, int m, float global_scale,
                                               void * c_bf16, int ldc, q35b_stream stream);
 

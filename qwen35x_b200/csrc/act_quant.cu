@@ -218,24 +218,39 @@ int launch_amax(const T * x, size_t n, unsigned int * ws, float * g_out, cudaStr
 
 }  // namespace
 
-int launch_quantize_bf16(const void * x, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
-                         float * g_dev, void * workspace, cudaStream_t s) {
+namespace {
+
+template <typename T>
+int launch_quantize_activations(const T * x, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
+                                float * g_dev, void * workspace, cudaStream_t s) {
   if (const int st = check_quant_args(x, m, k, codes, scales_tiled)) return st;
   if (g_dev == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 quantisation needs a device word for the input scale.");
-  const auto * xb = static_cast<const __nv_bfloat16 *>(x);
   const bool dynamic = !(global_scale > 0.0f);
   if (dynamic) {
     if (workspace == nullptr) return fail(Q35B_ERR_ARGUMENT, "Dynamic NVFP4 quantisation needs its workspace.");
-    if (const int st = launch_amax(xb, static_cast<size_t>(m) * k, static_cast<unsigned int *>(workspace), g_dev, s)) return st;
+    if (const int st = launch_amax(x, static_cast<size_t>(m) * k, static_cast<unsigned int *>(workspace), g_dev, s)) return st;
   }
   const int rows_padded = round_up_int(m, 128);
   const size_t threads = static_cast<size_t>(rows_padded) * ((((k >> 4) + 3) >> 2) << 2);
   const unsigned blocks = static_cast<unsigned>((threads + kThreads - 1) / kThreads);
-  quantize_nvfp4_kernel<__nv_bfloat16, kEngine, true><<<blocks, kThreads, 0, s>>>(
-    xb, m, rows_padded, k, dynamic ? g_dev : nullptr, global_scale, dynamic ? nullptr : g_dev, 0, codes, scales_tiled);
+  quantize_nvfp4_kernel<T, kEngine, true><<<blocks, kThreads, 0, s>>>(
+    x, m, rows_padded, k, dynamic ? g_dev : nullptr, global_scale, dynamic ? nullptr : g_dev, 0, codes, scales_tiled);
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "quantize_nvfp4_kernel launch");
   return Q35B_OK;
+}
+
+}  // namespace
+
+int launch_quantize_bf16(const void * x, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
+                         float * g_dev, void * workspace, cudaStream_t s) {
+  return launch_quantize_activations(static_cast<const __nv_bfloat16 *>(x), m, k, global_scale, codes, scales_tiled, g_dev,
+                                     workspace, s);
+}
+
+int launch_quantize_f32(const float * x, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
+                        float * g_dev, void * workspace, cudaStream_t s) {
+  return launch_quantize_activations(x, m, k, global_scale, codes, scales_tiled, g_dev, workspace, s);
 }
 
 int launch_quantize_reference_recipe(const void * x, int m, int k, int swap, uint8_t * codes, uint8_t * scales_tiled,

@@ -36,9 +36,27 @@ int sm_count() {
   return cached[dev];
 }
 
+int check_weight_device(const q35b_weight * w) {
+  int dev = -1;
+  Q35B_CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
+  if (w != nullptr && dev != w->device) {
+    return fail(Q35B_ERR_ARGUMENT, "NVFP4 weight lives on device " + std::to_string(w->device) + " but the current device is " +
+                                     std::to_string(dev) + ".");
+  }
+  return Q35B_OK;
+}
+
 namespace {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Host-only finishing touches of a new weight: tensor maps, and the library's default status word resolved on this
+// device so that no projection call has to do it (possibly under stream capture).
+int finish_weight(q35b_weight * w) {
+  if (const int st = build_weight_maps(w)) return st;
+  unsigned int * word = nullptr;
+  return default_status_word(&word);
+}
 
 int validate_dims(int n, int k, int shard_index, int shard_count) {
   if (n <= 0 || k <= 0 || (k % 16) != 0) {
@@ -152,6 +170,10 @@ int q35b_weight_create(const uint8_t * codes_host, const uint8_t * scales_host, 
     q35b_weight_destroy(w);
     return fail_cuda(e, "cudaMemcpy(nvfp4 weight)");
   }
+  if (const int st = finish_weight(w)) {
+    q35b_weight_destroy(w);
+    return st;
+  }
   *out = w;
   return Q35B_OK;
 }
@@ -199,6 +221,10 @@ int q35b_weight_create_from_device(const uint8_t * codes_dev, const uint8_t * sc
     return fail_cuda(e, "cudaStreamSynchronize(nvfp4 weight)");
   }
   w->negative_scales = flag != 0;
+  if (const int st = finish_weight(w)) {
+    q35b_weight_destroy(w);
+    return st;
+  }
   *out = w;
   return Q35B_OK;
 }
@@ -276,13 +302,19 @@ int q35b_gemv_w4a16_bf16(const q35b_weight * w, const void * x_bf16, int m, void
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15u) != 0) {
       return fail(Q35B_ERR_ARGUMENT, "Activations of the streaming NVFP4 projection must be 16-byte aligned.");
     }
+    if (const int st = check_weight_device(w)) return st;
     auto * wm = const_cast<q35b_weight *>(w);
-    if (wm->stream_batch[m] == nullptr) {
-      // first use with this token count: build (and upload) the single-projection work list
-      q35b_gemv_item item{w, nullptr, nullptr, nullptr, 0};
-      if (const int st = gemv_batch_build(&item, 1, m, &wm->stream_batch[m])) return st;
+    q35b_gemv_batch * batch = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(wm->batch_mutex);
+      if (wm->stream_batch[m] == nullptr) {
+        // first use with this token count: build (and upload) the single-projection work list
+        q35b_gemv_item item{w, nullptr, nullptr, nullptr, 0};
+        if (const int st = gemv_batch_build(&item, 1, m, &wm->stream_batch[m])) return st;
+      }
+      batch = wm->stream_batch[m];
     }
-    return gemv_batch_launch(wm->stream_batch[m], x_bf16, y_bf16, static_cast<cudaStream_t>(stream));
+    return gemv_batch_launch(batch, x_bf16, y_bf16, static_cast<cudaStream_t>(stream));
   }
   return launch_gemv_bf16(w, x_bf16, m, y_bf16, kernel, static_cast<cudaStream_t>(stream));
 }
@@ -324,6 +356,12 @@ int q35b_quantize_nvfp4_bf16(const void * x_bf16, int m, int k, float global_sca
                               static_cast<cudaStream_t>(stream));
 }
 
+int q35b_quantize_nvfp4_f32(const float * x_f32, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
+                            float * input_scale_dev, void * workspace, q35b_stream stream) {
+  return launch_quantize_f32(x_f32, m, k, global_scale, codes, scales_tiled, input_scale_dev, workspace,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int q35b_quantize_nvfp4_bf16_reference_recipe(const void * x_bf16, int m, int k, int swap_nibbles, uint8_t * codes,
                                               uint8_t * scales_tiled, q35b_stream stream) {
   return launch_quantize_reference_recipe(x_bf16, m, k, swap_nibbles, codes, scales_tiled,
@@ -338,7 +376,7 @@ int q35b_quantize_weight_f32(const float * w_f32, int n, int k, uint8_t * codes,
 int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
                         const float * input_scale_dev, int m, void * c_bf16, int ldc, unsigned int * status_dev,
                         q35b_stream stream) {
-  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, c_bf16, ldc, nullptr, 0,
+  return launch_gemm_w4a4(w, a_codes, a_scales_tiled, input_scale_dev, m, c_bf16, ldc, nullptr, 0,
                           status_dev, static_cast<cudaStream_t>(stream));
 }
 
@@ -346,7 +384,7 @@ int q35b_gemm_w4a4_gate_up_nvfp4(const q35b_weight * w, const uint8_t * a_codes,
                                  const float * input_scale_dev, int m, uint8_t * out_codes, uint8_t * out_scales_tiled,
                                  const float * out_scale_dev, unsigned int * status_dev, q35b_stream stream) {
   const GemmQuantOut q{out_codes, out_scales_tiled, out_scale_dev};
-  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, nullptr, 0, nullptr, 0,
+  return launch_gemm_w4a4(w, a_codes, a_scales_tiled, input_scale_dev, m, nullptr, 0, nullptr, 0,
                           status_dev, static_cast<cudaStream_t>(stream), &q);
 }
 
@@ -354,7 +392,7 @@ int q35b_gemm_w4a4_bf16_residual(const q35b_weight * w, const uint8_t * a_codes,
                                  const float * input_scale_dev, int m, const void * residual_bf16, int ldr, void * c_bf16,
                                  int ldc, unsigned int * status_dev, q35b_stream stream) {
   if (residual_bf16 == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection received a null residual.");
-  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, c_bf16, ldc,
+  return launch_gemm_w4a4(w, a_codes, a_scales_tiled, input_scale_dev, m, c_bf16, ldc,
                           residual_bf16, ldr, status_dev, static_cast<cudaStream_t>(stream));
 }
 

@@ -6,6 +6,7 @@
 
 #include <atomic>
 #include <cstdint>
+#include <mutex>
 #include <string>
 
 #include "../../include/q35b_nvfp4.h"
@@ -28,6 +29,10 @@ inline void count_launch(unsigned n = 1) { g_launches.fetch_add(n, std::memory_o
 
 int sm_count();
 
+// Q35B_OK when the weight lives on the calling thread's current device, else Q35B_ERR_ARGUMENT: every launch goes
+// to the current device, and a weight of another GPU would be read through a pointer that device cannot reach.
+int check_weight_device(const struct ::q35b_weight * w);
+
 }  // namespace q35b
 
 // One projection weight on the device.  All three arrays live in a single
@@ -48,11 +53,15 @@ struct q35b_weight {
   uint8_t * scales_tiled = nullptr; // [ceil128(rows), ceil4(k/16)] 128x4 tiles (UMMA scale factors)
   size_t codes_bytes = 0, scales_bytes = 0, scales_tiled_bytes = 0;
   bool negative_scales = false;      // some block scale has its sign bit set (only the SIMT decode kernel takes those)
-  struct q35b_gemv_batch * stream_batch[9] = {nullptr};  // lazily built single-projection work lists, by token count
-  bool has_tmap = false;
-  alignas(64) CUtensorMap tmap_codes;  // 2-D map over codes for the GEMM's B tiles
-  int tmap_block_n = 0;
-  bool has_tmap2 = false;              // maps of the 2-CTA GEMM: 128-row code boxes and 4-chunk scale boxes
+  // Single-projection work lists of the streaming decode kernel, by token count: built on first use under
+  // batch_mutex (the only state of a weight that changes after q35b_weight_create*).
+  struct q35b_gemv_batch * stream_batch[9] = {nullptr};
+  std::mutex batch_mutex;
+  // Tensor maps of the GEMMs, encoded once at creation (build_weight_maps): B tiles of the 1-CTA kernel in its two
+  // widths, and the 2-CTA kernel's 96-row code boxes and 4-chunk scale boxes.
+  bool has_maps = false;
+  alignas(64) CUtensorMap tmap_codes_128;
+  alignas(64) CUtensorMap tmap_codes_256;
   alignas(64) CUtensorMap tmap2_codes;
   alignas(64) CUtensorMap tmap2_sf;
 };
@@ -67,6 +76,8 @@ int launch_gemv_f32(const q35b_weight * w, const float * x, float input_scale, f
 // act_quant.cu
 int launch_quantize_bf16(const void * x, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
                          float * g_dev, void * workspace, cudaStream_t s);
+int launch_quantize_f32(const float * x, int m, int k, float global_scale, uint8_t * codes, uint8_t * scales_tiled,
+                        float * g_dev, void * workspace, cudaStream_t s);
 int launch_quantize_reference_recipe(const void * x, int m, int k, int swap, uint8_t * codes, uint8_t * scales_tiled,
                                      cudaStream_t s);
 int launch_quantize_weight_f32(const float * w, int n, int k, uint8_t * codes, uint8_t * scales_rowmajor,
@@ -100,7 +111,13 @@ struct GemmGather {
   unsigned int * done_counter = nullptr;
   unsigned int epoch = 0;
 };
-int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+// Encodes the weight's tensor maps (host only, no device work); called by q35b_weight_create*.
+int build_weight_maps(q35b_weight * w);
+// The library's own status word of the current device (a file-scope device variable): what the GEMM entry points
+// use when the caller passes no status word.  Resolved once per device; q35b_weight_create* calls it so that the
+// first projection does not have to.
+int default_status_word(unsigned int ** out);
+int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
                      cudaStream_t s, const GemmQuantOut * qout = nullptr, const GemmGather * gather = nullptr);
 
@@ -108,7 +125,8 @@ int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a
 // gemm_w4a4_2cta.cu
 bool gemm_2cta_eligible(const q35b_weight * w, int m);
 struct GemmEpilogue;
-int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+int make_sf_map(CUtensorMap * map, const void * base, long long chunks);
+int launch_gemm_w4a4_2cta(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                           int m, void * c_bf16, int ldc, const GemmEpilogue & ep, unsigned int * status_dev,
                           cudaStream_t s);
 

@@ -40,6 +40,7 @@ struct GemmEpilogue {
   // grid has stored, its last CTA writes `epoch` into this rank's flag slot on every rank (peer_flag[i]).
   static constexpr int kMaxPeers = 7;
   int n_peers = 0;
+  int forward_rows = 0;  // host-checked: ldc, the column count and every matrix base allow 32-byte row pieces
   __nv_bfloat16 * peer_c[kMaxPeers] = {};
   unsigned int * peer_flag[kMaxPeers] = {};
   unsigned int * done_counter = nullptr;   // this rank's, zero between launches
@@ -55,8 +56,9 @@ __device__ __forceinline__ void st_global_v8(void * p, const uint32_t (&v)[8]) {
 // A warp that has just stored 32 rows x COLS BF16 columns of the local matrix (one row per lane) sends them to the
 // other ranks as whole lines: it reads its rows back from L2 with four lanes per 128 bytes and repeats them with the
 // same lane mapping, so every store instruction covers whole 128-byte lines of a few rows, the unit NVLink moves
-// well, instead of thirty-two 32-byte pieces of thirty-two rows.  col0 and n are multiples of 16 (row shards are
-// cut on 128-row boundaries); pieces past column n or row m are skipped.
+// well, instead of thirty-two 32-byte pieces of thirty-two rows.  Only taken when the host found ldc, n and the
+// matrix bases to be multiples of 16 elements (GemmEpilogue::forward_rows); otherwise every lane repeats its own
+// stores on the peers.  Pieces past column n or row m are skipped.
 template <int COLS>
 __device__ __forceinline__ void gemm_forward_rows_to_peers(const GemmEpilogue & ep, const __nv_bfloat16 * c, int ldc,
                                                            int row0, int m, int col0, int n, int lane) {

@@ -357,7 +357,7 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       if (lane == 0) mbar_arrive(smem_u32(drained + ab));
       // plain BF16 output of a gathering launch: store locally, then forward whole rows; the fused epilogues (and a
       // launch without peers) store per lane
-      const bool forward = ep.n_peers > 0 && !ep.gate_up;
+      const bool forward = ep.n_peers > 0 && !ep.gate_up && ep.forward_rows != 0;
       if (row < m) {
 #pragma unroll
         for (int j = 0; j < kEpiCols / 32; ++j) {
@@ -381,6 +381,8 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                  : "memory");
   }
 }
+
+}  // namespace
 
 // 2-D map over a tiled scale array seen as [chunks, 128 x u32]: box = 4 consecutive 512-byte chunks.
 int make_sf_map(CUtensorMap * map, const void * base, long long chunks) {
@@ -409,26 +411,29 @@ int make_sf_map(CUtensorMap * map, const void * base, long long chunks) {
   return Q35B_OK;
 }
 
-}  // namespace
+int build_weight_maps(q35b_weight * w) {
+  if (w->rows <= 0 || (w->k % 64) != 0) return Q35B_OK;  // such a weight never reaches a GEMM
+  if (const int st = make_code_map(&w->tmap_codes_128, w->codes, w->rows, w->k / 2, 128)) return st;
+  if (const int st = make_code_map(&w->tmap_codes_256, w->codes, w->rows, w->k / 2, 256)) return st;
+  if (const int st = make_code_map(&w->tmap2_codes, w->codes, w->rows, w->k / 2, kCtaBRows)) return st;
+  const long long chunks = static_cast<long long>((w->rows + 127) / 128) * (w->k / 64);
+  if (const int st = make_sf_map(&w->tmap2_sf, w->scales_tiled, chunks)) return st;
+  w->has_maps = true;
+  return Q35B_OK;
+}
 
 bool gemm_2cta_eligible(const q35b_weight * w, int m) {
   return w->rows >= 192 && m >= 256 && (w->k % 64) == 0;
 }
 
-int launch_gemm_w4a4_2cta(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+int launch_gemm_w4a4_2cta(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                           int m, void * c_bf16, int ldc, const GemmEpilogue & ep, unsigned int * status_dev,
                           cudaStream_t s) {
-  static bool attr_set[64] = {false};
-  if (!attr_set[w->device & 63]) {
+  static std::atomic<bool> attr_set[64];
+  if (!attr_set[w->device & 63].load(std::memory_order_acquire)) {
     Q35B_CUDA_TRY(cudaFuncSetAttribute(gemm_w4a4_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
                   "cudaFuncSetAttribute(2-CTA gemm smem)");
-    attr_set[w->device & 63] = true;
-  }
-  if (!w->has_tmap2) {
-    if (const int st = make_code_map(&w->tmap2_codes, w->codes, w->rows, w->k / 2, kCtaBRows)) return st;
-    const long long chunks = static_cast<long long>((w->rows + 127) / 128) * (w->k / 64);
-    if (const int st = make_sf_map(&w->tmap2_sf, w->scales_tiled, chunks)) return st;
-    w->has_tmap2 = true;
+    attr_set[w->device & 63].store(true, std::memory_order_release);
   }
   CUtensorMap tmap_a, tmap_sfa;
   if (const int st = make_code_map(&tmap_a, a_codes, m, w->k / 2, kCtaRows)) return st;

@@ -377,33 +377,63 @@ int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, i
 namespace {
 
 template <int BLOCK_N>
-int launch_tile(q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_scales, const float * g_dev, int m,
+int launch_tile(const q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t * a_scales, const float * g_dev, int m,
                 void * c, int ldc, const GemmEpilogue & ep, unsigned int * status, cudaStream_t s) {
   using C = Cfg<BLOCK_N>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];
   auto kernel = gemm_w4a4_tcgen05_kernel<BLOCK_N>;
-  if (!attr_set[w->device & 63]) {
+  if (!attr_set[w->device & 63].load(std::memory_order_acquire)) {
+    // idempotent, so two threads getting here together is harmless
     Q35B_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes),
                   "cudaFuncSetAttribute(gemm smem)");
-    attr_set[w->device & 63] = true;
-  }
-  if (!w->has_tmap || w->tmap_block_n != BLOCK_N) {
-    if (const int st = make_code_map(&w->tmap_codes, w->codes, w->rows, w->k / 2, BLOCK_N)) return st;
-    w->has_tmap = true;
-    w->tmap_block_n = BLOCK_N;
+    attr_set[w->device & 63].store(true, std::memory_order_release);
   }
   const dim3 grid((w->rows + BLOCK_N - 1) / BLOCK_N, (m + kBlockM - 1) / kBlockM);
-  kernel<<<grid, kThreads, C::kSmemBytes, s>>>(tmap_a, w->tmap_codes, a_scales, w->scales_tiled, g_dev, ep, m,
-                                               w->rows, w->k / 2, (w->rows + 127) / 128,
+  kernel<<<grid, kThreads, C::kSmemBytes, s>>>(tmap_a, BLOCK_N == 256 ? w->tmap_codes_256 : w->tmap_codes_128, a_scales,
+                                               w->scales_tiled, g_dev, ep, m, w->rows, w->k / 2, (w->rows + 127) / 128,
                                                static_cast<__nv_bfloat16 *>(c), ldc, status);
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "gemm_w4a4_tcgen05_kernel launch");
   return Q35B_OK;
 }
 
+// What the GEMM entry points use as *status when the caller passes none: one word per device inside the library
+// (no allocation anywhere on that path).
+__device__ unsigned int g_default_status;
+
 }  // namespace
 
-int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+int default_status_word(unsigned int ** out) {
+  static std::mutex mutex;
+  static unsigned int * word[64] = {nullptr};
+  int dev = 0;
+  Q35B_CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(Q35B_ERR_ARGUMENT, "Device ordinal out of range.");
+  std::lock_guard<std::mutex> lock(mutex);
+  if (word[dev] == nullptr) {
+    // the symbol's name is only a handle in host code; its address on the current device comes from the runtime
+    void * p = nullptr;
+    Q35B_CUDA_TRY(cudaGetSymbolAddress(&p, g_default_status), "cudaGetSymbolAddress(default status word)");
+    word[dev] = static_cast<unsigned int *>(p);
+  }
+  *out = word[dev];
+  return Q35B_OK;
+}
+
+}  // namespace q35b
+
+extern "C" int q35b_gemm_default_status(unsigned int * status_out) {
+  using namespace q35b;
+  if (status_out == nullptr) return fail(Q35B_ERR_ARGUMENT, "Null status pointer.");
+  unsigned int * word = nullptr;
+  if (const int st = default_status_word(&word)) return st;
+  Q35B_CUDA_TRY(cudaMemcpy(status_out, word, sizeof(unsigned int), cudaMemcpyDeviceToHost), "cudaMemcpy(default status word)");
+  return Q35B_OK;
+}
+
+namespace q35b {
+
+int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
                      int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
                      cudaStream_t s, const GemmQuantOut * qout, const GemmGather * gather) {
   if (w == nullptr || a_codes == nullptr || a_scales_tiled == nullptr || g_dev == nullptr ||
@@ -447,21 +477,22 @@ int launch_gemm_w4a4(q35b_weight * w, const uint8_t * a_codes, const uint8_t * a
     }
     ep.done_counter = gather->done_counter;
     ep.epoch = gather->epoch;
+    // whole-row forwarding moves aligned 32-byte pieces; any other geometry takes the per-lane peer stores
+    bool aligned = (ldc % 16) == 0 && (out_cols % 16) == 0 && (reinterpret_cast<uintptr_t>(c_bf16) & 31u) == 0;
+    for (int i = 0; i < gather->n_peers; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(gather->peer_c[i]) & 31u) == 0;
+    ep.forward_rows = aligned ? 1 : 0;
   }
   if ((w->k % 64) != 0) return fail(Q35B_ERR_SHAPE, "NVFP4 W4A4 GEMM needs cols to be a multiple of 64.");
   if ((reinterpret_cast<uintptr_t>(a_codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a_scales_tiled) & 15u) != 0) {
     return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection buffers must be 16-byte aligned.");
   }
   if (w->rows == 0) return Q35B_OK;
-  static unsigned int * fallback_status[64] = {nullptr};
+  if (const int st = check_weight_device(w)) return st;
+  if (!w->has_maps) return fail(Q35B_ERR_ARGUMENT, "NVFP4 weight has no tensor maps (it was not built by q35b_weight_create*).");
   if (status_dev == nullptr) {
-    unsigned int *& slot = fallback_status[w->device & 63];
-    if (slot == nullptr) {
-      Q35B_CUDA_TRY(cudaMalloc(&slot, sizeof(unsigned int)), "cudaMalloc(gemm status)");
-      Q35B_CUDA_TRY(cudaMemset(slot, 0, sizeof(unsigned int)), "cudaMemset(gemm status)");
-    }
-    status_dev = slot;
-    Q35B_CUDA_TRY(cudaMemsetAsync(slot, 0, sizeof(unsigned int), s), "cudaMemsetAsync(gemm status)");
+    // the library's own word, cleared on the stream ahead of the launch (a memset node under stream capture)
+    if (const int st = default_status_word(&status_dev)) return st;
+    Q35B_CUDA_TRY(cudaMemsetAsync(status_dev, 0, sizeof(unsigned int), s), "cudaMemsetAsync(gemm status)");
   }
   // Large problems: pairs of CTAs on 256 x 256 tiles, persistent (gemm_w4a4_2cta.cu).
   if (gemm_2cta_eligible(w, m)) {

@@ -246,6 +246,11 @@ int launch_any(const q35b_weight * w, const XT * x, int m, OT * y, float x_scale
   if (kernel != Q35B_GEMV_AUTO && kernel != Q35B_GEMV_SIMT && kernel != Q35B_GEMV_STREAM) {
     return fail(Q35B_ERR_ARGUMENT, "Unknown NVFP4 projection kernel id " + std::to_string(kernel) + ".");
   }
+  if (const int st = check_weight_device(w)) return st;
+  if ((w->k % 32) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) != 0) {
+    // the vector kernel reads activations with 16-byte loads
+    return fail(Q35B_ERR_ARGUMENT, "Activations of the NVFP4 projection must be 16-byte aligned.");
+  }
   if ((w->k % 32) != 0) {
     const int blocks = (w->rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
     gemv_w4a16_generic_kernel<XT, OT><<<blocks, kThreads, 0, s>>>(w->codes, w->scales, x, y, w->rows, w->k, m,
@@ -271,6 +276,7 @@ int launch_any(const q35b_weight * w, const XT * x, int m, OT * y, float x_scale
 int launch_dequant_bf16(const q35b_weight * w, void * w_bf16, cudaStream_t s) {
   if (w == nullptr || w_bf16 == nullptr) return fail(Q35B_ERR_ARGUMENT, "NVFP4 dequantisation received a null buffer.");
   if ((reinterpret_cast<uintptr_t>(w_bf16) & 15u) != 0) return fail(Q35B_ERR_ARGUMENT, "NVFP4 dequantisation output must be 16-byte aligned.");
+  if (const int st = check_weight_device(w)) return st;
   if (w->rows == 0) return Q35B_OK;
   const size_t blocks16 = static_cast<size_t>(w->rows) * (w->k / 16);
   dequant_bf16_kernel<<<static_cast<unsigned>((blocks16 + kThreads - 1) / kThreads), kThreads, 0, s>>>(

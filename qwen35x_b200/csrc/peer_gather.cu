@@ -51,6 +51,12 @@ __global__ void peer_gather_wait_kernel(const unsigned int * flags, int world, i
   atomicExch(status, kStatusGatherWait);
 }
 
+// A rank whose shard is empty (more ranks than 128-row blocks) computes nothing but still has to tell the others
+// that its part of the epoch is complete.
+__global__ void peer_signal_kernel(GemmEpilogue ep) {
+  if (threadIdx.x < ep.n_peers) *reinterpret_cast<volatile unsigned int *>(ep.peer_flag[threadIdx.x]) = ep.epoch;
+}
+
 }  // namespace
 }  // namespace q35b
 
@@ -140,9 +146,19 @@ int q35b_gemm_w4a4_bf16_allgather(const q35b_weight * w, const uint8_t * a_codes
   gather.done_counter = flag_words(buffers[rank]) + kMaxRanks;
   gather.epoch = epoch;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w->rows == 0) {
+    GemmEpilogue ep;
+    ep.n_peers = gather.n_peers;
+    for (int i = 0; i < gather.n_peers; ++i) ep.peer_flag[i] = gather.peer_flag[i];
+    ep.epoch = epoch;
+    peer_signal_kernel<<<1, 32, 0, s>>>(ep);
+    count_launch();
+    Q35B_CUDA_TRY(cudaGetLastError(), "peer_signal_kernel launch");
+    return Q35B_OK;
+  }
   Q35B_CUDA_TRY(cudaMemsetAsync(gather.done_counter, 0, sizeof(unsigned int), s), "cudaMemsetAsync(gather counter)");
   auto * c = reinterpret_cast<__nv_bfloat16 *>(buffers[rank]->base) + col0;
-  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), a_codes, a_scales_tiled, input_scale_dev, m, c, ldc, nullptr, 0,
+  return launch_gemm_w4a4(w, a_codes, a_scales_tiled, input_scale_dev, m, c, ldc, nullptr, 0,
                           status_dev, s, nullptr, &gather);
 }
 

@@ -70,6 +70,7 @@ int q35b_project_prefill_bf16_static(const q35b_weight * w, const void * x_bf16,
                   ". Split the tokens into smaller chunks or use q35b_quantize_nvfp4_bf16 + q35b_gemm_w4a4_bf16 with "
                   "caller-owned scratch.");
   }
+  if (const int st = check_weight_device(w)) return st;
   unsigned char * base = nullptr;
   if (const int st = scratch_for_current_device(&base)) return st;
   auto s = static_cast<cudaStream_t>(stream);
@@ -82,7 +83,15 @@ int q35b_project_prefill_bf16_static(const q35b_weight * w, const void * x_bf16,
   uint8_t * codes = base + kControlBytes;
   uint8_t * scales = codes + codes_bytes;
   if (const int st = launch_quantize_bf16(x_bf16, m, w->k, global_scale, codes, scales, g_dev, workspace, s)) return st;
-  return launch_gemm_w4a4(const_cast<q35b_weight *>(w), codes, scales, g_dev, m, c_bf16, ldc, nullptr, 0, status, s);
+  return launch_gemm_w4a4(w, codes, scales, g_dev, m, c_bf16, ldc, nullptr, 0, status, s);
+}
+
+int q35b_static_prefill_status(unsigned int * status_out) {
+  if (status_out == nullptr) return fail(Q35B_ERR_ARGUMENT, "Null status pointer.");
+  unsigned char * base = nullptr;
+  if (const int st = scratch_for_current_device(&base)) return st;
+  Q35B_CUDA_TRY(cudaMemcpy(status_out, base + 32, sizeof(unsigned int), cudaMemcpyDeviceToHost), "cudaMemcpy(prefill scratch status)");
+  return Q35B_OK;
 }
 
 }  // extern "C"

@@ -75,6 +75,12 @@ def lib() -> C.CDLL:
     L.q35b_quant_workspace_bytes.restype = sz
     L.q35b_quantize_nvfp4_bf16.restype = i
     L.q35b_quantize_nvfp4_bf16.argtypes = [vp, i, i, f, vp, vp, vp, vp, vp]
+    L.q35b_quantize_nvfp4_f32.restype = i
+    L.q35b_quantize_nvfp4_f32.argtypes = [vp, i, i, f, vp, vp, vp, vp, vp]
+    L.q35b_gemm_default_status.restype = i
+    L.q35b_gemm_default_status.argtypes = [C.POINTER(C.c_uint)]
+    L.q35b_static_prefill_status.restype = i
+    L.q35b_static_prefill_status.argtypes = [C.POINTER(C.c_uint)]
     L.q35b_quantize_nvfp4_bf16_reference_recipe.restype = i
     L.q35b_quantize_nvfp4_bf16_reference_recipe.argtypes = [vp, i, i, i, vp, vp, vp]
     L.q35b_quantize_weight_f32.restype = i
@@ -330,15 +336,30 @@ def act_scratch(m: int, k: int, device):
 
 
 def quantize_activations(x, global_scale: float = 0.0, scratch=None):
-    """BF16 [m, k] -> (codes [m, k/2] u8, tiled scales u8, g fp32[1]) on the device."""
+    """BF16 (or fp32) [m, k] -> (codes [m, k/2] u8, tiled scales u8, g fp32[1]) on the device."""
     torch = _torch()
-    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 2
+    assert x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.is_contiguous() and x.dim() == 2
     m, k = x.shape
     codes, scales, g = scratch if scratch is not None else act_scratch(m, k, x.device)
     ws = _workspace(torch, x.device)
-    _check(lib().q35b_quantize_nvfp4_bf16(x.data_ptr(), m, k, global_scale, codes.data_ptr(), scales.data_ptr(),
-                                          g.data_ptr(), ws.data_ptr(), _stream_ptr(torch)))
+    fn = lib().q35b_quantize_nvfp4_bf16 if x.dtype == torch.bfloat16 else lib().q35b_quantize_nvfp4_f32
+    _check(fn(x.data_ptr(), m, k, global_scale, codes.data_ptr(), scales.data_ptr(), g.data_ptr(), ws.data_ptr(),
+              _stream_ptr(torch)))
     return codes.view(m, k // 2), scales, g
+
+
+def gemm_default_status() -> int:
+    """The library's own GEMM status word of the current device (used when a call passes no status word)."""
+    out = C.c_uint(0)
+    _check(lib().q35b_gemm_default_status(C.byref(out)))
+    return int(out.value)
+
+
+def static_prefill_status() -> int:
+    """Status word of the built-in prefill scratch of the current device (see project_prefill_static)."""
+    out = C.c_uint(0)
+    _check(lib().q35b_static_prefill_status(C.byref(out)))
+    return int(out.value)
 
 
 def quantize_activations_reference_recipe(x, swap_nibbles: bool = True):

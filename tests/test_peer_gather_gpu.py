@@ -1,7 +1,9 @@
 """The N-sharded prefill projection whose GEMM stores are the all-gather (q35b_gemm_w4a4_bf16_allgather).
 On one GPU the ranks are emulated in one process: every rank's shard GEMM is launched first, the waits afterwards,
 so no launch ever waits for a later one.  With two or more GPUs a torchrun job runs the real thing over CUDA IPC.
-Reference: the unsharded GEMM of the same library (bit-identical columns) and the oracle (relative L2 <= 1e-3)."""
+Reference: the unsharded GEMM of the same library (bit-identical columns) and the oracle (relative L2 <= 1e-3).
+N = 1000 and N = 200 give a last shard and a row stride that are not multiples of 16 elements: the remote stores
+then go lane by lane instead of as whole forwarded rows."""
 import os
 import subprocess
 import sys
@@ -17,7 +19,7 @@ REL_L2_TOL = 1e-3
 
 
 @pytest.mark.parametrize("world,m,n,k", [(2, 300, 1024, 512), (3, 64, 1152, 256), (4, 257, 2560, 512), (8, 130, 2048, 256),
-                                         (8, 300, 3584, 512)])
+                                         (8, 300, 3584, 512), (2, 300, 1000, 512), (3, 40, 200, 256)])
 def test_emulated_ranks_fill_every_matrix(engine, oracle, world, m, n, k):
     import torch
 
