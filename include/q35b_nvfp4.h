@@ -111,7 +111,14 @@ Q35B_API int q35b_weight_create_gate_up(const uint8_t * gate_codes_host, const u
                                         float gate_weight_scale_2, const uint8_t * up_codes_host,
                                         const uint8_t * up_scales_host, float up_weight_scale_2, int n_half, int k,
                                         q35b_weight ** out);
-/* 1 if the weight was built by q35b_weight_create_gate_up. */
+/* Row shard of such a pair, for the N-sharded prefill MLP: the interleaved matrix (2 * n_half rows) is cut like any
+ * other weight (q35b_shard_range(2 * n_half, ...), 128-row blocks), so shard i yields the output columns
+ * [row_begin / 2, row_begin / 2 + rows / 2) of silu(gate) * up, a multiple of 64 of them. */
+Q35B_API int q35b_weight_create_gate_up_shard(const uint8_t * gate_codes_host, const uint8_t * gate_scales_host,
+                                              float gate_weight_scale_2, const uint8_t * up_codes_host,
+                                              const uint8_t * up_scales_host, float up_weight_scale_2, int n_half,
+                                              int k, int shard_index, int shard_count, q35b_weight ** out);
+/* 1 if the weight was built by q35b_weight_create_gate_up(_shard). */
 Q35B_API int q35b_weight_is_gate_up(const q35b_weight * w);
 
 /* NVFP4 -> BF16 dequantisation of the whole weight, w_bf16 [rows, K] device: bf16(e2m1 * (e4m3 * s2)), the
@@ -252,7 +259,10 @@ Q35B_API int q35b_gemm_w4a4_bf16_residual(const q35b_weight * w, const uint8_t *
  * src/runtime/cuda_bench.cu:2621-2660).  out_scale_dev is that activation's per-tensor scale and must be known
  * in advance (the checkpoint's input_scale of the down projection, or amax / 2688 from a calibration run); values
  * beyond 2688 * scale saturate.  The bits equal q35b_quantize_nvfp4_bf16 applied, with the same scale, to the BF16
- * output of q35b_gemm_w4a4_bf16 on the same weight.  w must be a gate/up weight with rows/2 a multiple of 64. */
+ * output of q35b_gemm_w4a4_bf16 on the same weight.  w must be a gate/up weight with rows/2 a multiple of 64.
+ * out_codes / out_scales_tiled always describe the WHOLE activation [m, n_half]: a shard
+ * (q35b_weight_create_gate_up_shard) writes only its own columns of it, code bytes [row_begin / 4, ...) of every
+ * row and the matching scale tiles, so that the shards of all ranks together fill one activation. */
 Q35B_API int q35b_gemm_w4a4_gate_up_nvfp4(const q35b_weight * w, const uint8_t * a_codes,
                                           const uint8_t * a_scales_tiled, const float * input_scale_dev, int m,
                                           uint8_t * out_codes, uint8_t * out_scales_tiled,
@@ -285,6 +295,24 @@ Q35B_API int q35b_gemm_w4a4_bf16_allgather(const q35b_weight * w, const uint8_t 
                                            q35b_stream stream);
 Q35B_API int q35b_peer_gather_wait(q35b_peer_buffer * const * buffers, int world, int rank, unsigned int epoch,
                                    unsigned int * status_dev, q35b_stream stream);
+
+/* Pushes regions of this rank's peer buffer into the same place of every other rank's buffer (plain peer-memory
+ * stores over NVLink, 16 bytes per thread, whole 128-byte lines per warp) and then writes `epoch` into this rank's
+ * flag slot on every rank: q35b_peer_gather_wait(.., epoch, ..) on the receiving side returns when all ranks'
+ * pushes of that epoch have arrived.  It is the exchange step for outputs whose producer writes pieces too small to
+ * forward itself: the NVFP4 codes and scale tiles of q35b_gemm_w4a4_gate_up_nvfp4 on a shard (an N-sharded MLP
+ * block gathers 0.5625 bytes per intermediate element instead of 2), or a narrow BF16 shard.
+ * A region is `rows` rows of `row_bytes` bytes, `ld_bytes` apart, starting `offset` bytes into the buffer's data;
+ * all three multiples of 16; at most 4 regions per call.  Replaces the ncclAllGather of the row-sharded projection
+ * where the data is not one contiguous slab per rank. */
+typedef struct q35b_peer_region {
+  size_t offset;
+  size_t row_bytes;
+  size_t ld_bytes;
+  int rows;
+} q35b_peer_region;
+Q35B_API int q35b_peer_push(q35b_peer_buffer * const * buffers, int world, int rank, const q35b_peer_region * regions,
+                            int n_regions, unsigned int epoch, q35b_stream stream);
 
 /* Prefill projection for callers that cannot allocate device memory (no counterpart in the reference, whose
  * bridges all take caller-allocated scratch, include/qwen35x/runtime/cuda_bench.h:70-83).

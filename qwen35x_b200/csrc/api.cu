@@ -232,13 +232,21 @@ int q35b_weight_create_from_device(const uint8_t * codes_dev, const uint8_t * sc
 int q35b_weight_create_gate_up(const uint8_t * gate_codes_host, const uint8_t * gate_scales_host, float gate_weight_scale_2,
                                const uint8_t * up_codes_host, const uint8_t * up_scales_host, float up_weight_scale_2,
                                int n_half, int k, q35b_weight ** out) {
+  return q35b_weight_create_gate_up_shard(gate_codes_host, gate_scales_host, gate_weight_scale_2, up_codes_host,
+                                          up_scales_host, up_weight_scale_2, n_half, k, 0, 1, out);
+}
+
+int q35b_weight_create_gate_up_shard(const uint8_t * gate_codes_host, const uint8_t * gate_scales_host,
+                                     float gate_weight_scale_2, const uint8_t * up_codes_host,
+                                     const uint8_t * up_scales_host, float up_weight_scale_2, int n_half, int k,
+                                     int shard_index, int shard_count, q35b_weight ** out) {
   if (gate_codes_host == nullptr || gate_scales_host == nullptr || up_codes_host == nullptr || up_scales_host == nullptr ||
       out == nullptr) {
     return fail(Q35B_ERR_ARGUMENT, "NVFP4 weight creation received a null buffer.");
   }
   *out = nullptr;
   if (n_half <= 0 || (n_half % 8) != 0) return fail(Q35B_ERR_SHAPE, "A gate/up weight needs a row count that is a multiple of 8.");
-  if (const int st = validate_dims(2 * n_half, k, 0, 1)) return st;
+  if (const int st = validate_dims(2 * n_half, k, shard_index, shard_count)) return st;
   // rows alternate in groups of eight: 8 gate rows, 8 up rows, ...
   const size_t code_row = static_cast<size_t>(k) / 2, scale_row = static_cast<size_t>(k) / 16;
   std::vector<uint8_t> codes(2 * static_cast<size_t>(n_half) * code_row), scales(2 * static_cast<size_t>(n_half) * scale_row);
@@ -249,7 +257,10 @@ int q35b_weight_create_gate_up(const uint8_t * gate_codes_host, const uint8_t * 
     std::memcpy(&scales[(2 * grp + 1) * 8 * scale_row], up_scales_host + static_cast<size_t>(grp) * 8 * scale_row, 8 * scale_row);
   }
   q35b_weight * w = nullptr;
-  if (const int st = q35b_weight_create(codes.data(), scales.data(), gate_weight_scale_2, 1.0f, 2 * n_half, k, 0, 1, &w)) return st;
+  if (const int st = q35b_weight_create(codes.data(), scales.data(), gate_weight_scale_2, 1.0f, 2 * n_half, k, shard_index,
+                                        shard_count, &w)) {
+    return st;
+  }
   w->gate_up = true;
   w->s2_up = up_weight_scale_2;
   *out = w;
@@ -383,7 +394,7 @@ int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes, const ui
 int q35b_gemm_w4a4_gate_up_nvfp4(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
                                  const float * input_scale_dev, int m, uint8_t * out_codes, uint8_t * out_scales_tiled,
                                  const float * out_scale_dev, unsigned int * status_dev, q35b_stream stream) {
-  const GemmQuantOut q{out_codes, out_scales_tiled, out_scale_dev};
+  const GemmQuantOut q{out_codes, out_scales_tiled, out_scale_dev, w != nullptr ? w->n_total / 2 : 0};
   return launch_gemm_w4a4(w, a_codes, a_scales_tiled, input_scale_dev, m, nullptr, 0, nullptr, 0,
                           status_dev, static_cast<cudaStream_t>(stream), &q);
 }

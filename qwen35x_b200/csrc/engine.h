@@ -97,9 +97,10 @@ size_t gemv_batch_bytes(const struct q35b_gemv_batch * b);
 int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, int box_rows);
 // Where a gate/up GEMM writes silu(gate) * up as an NVFP4 activation instead of BF16 (see gemm_epilogue.cuh).
 struct GemmQuantOut {
-  uint8_t * codes;          // [m, rows / 4] bytes
-  uint8_t * scales_tiled;   // tiled block scales of the [m, rows / 2] activation
+  uint8_t * codes;          // [m, total_cols / 2] bytes: the whole activation, of which this weight writes its columns
+  uint8_t * scales_tiled;   // tiled block scales of the [m, total_cols] activation
   const float * g_dev;      // its per-tensor scale, known in advance
+  int total_cols;           // width of the whole activation (= rows / 2 for an unsharded gate/up weight)
 };
 // Where a gathering GEMM repeats its stores on the other ranks and signals completion (see gemm_epilogue.cuh,
 // peer_gather.cu).  Pointers are this process's mappings of the other ranks' buffers, already moved to the shard's

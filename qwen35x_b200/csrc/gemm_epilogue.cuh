@@ -35,6 +35,11 @@ struct GemmEpilogue {
   uint8_t * q_scales = nullptr;
   const float * q_g = nullptr;
   int q_slots = 0;
+  // The NVFP4 output may be a column range of a wider activation (a row shard of the gate/up weight writing its
+  // part of [m, intermediate]): q_codes already points at the range's first code byte, q_ld is the byte stride
+  // between rows, q_slot0 the first scale column of the range and q_slots the scale columns of the whole width.
+  int q_ld = 0;
+  int q_slot0 = 0;
   // Gather fused into the stores (multi-GPU, rows sharded): every BF16 store is repeated into the same place of
   // the full output matrix on each other rank (peer_c[i], plain peer-memory stores over NVLink), and when the whole
   // grid has stored, its last CTA writes `epoch` into this rank's flag slot on every rank (peer_flag[i]).
@@ -127,9 +132,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // of the whole problem (weight rows); g = the activation tensor's scale.
 // to_peers: also repeat every store on the other ranks (one 32-byte piece per lane); a caller that forwards whole
 // rows afterwards (gemm_forward_rows_to_peers) passes false.
+// q_g: value of *ep.q_g (the NVFP4 output's per-tensor scale), read once per warp by the caller: thousands of warps
+// loading that one word per chunk would queue up on a single L2 slice.
 __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int row, int col0, int n, float g,
                                                    const GemmEpilogue & ep, __nv_bfloat16 * __restrict__ c, int ldc,
-                                                   bool to_peers = true) {
+                                                   bool to_peers = true, float q_g = 1.0f) {
   if (col0 >= n) return;  // a chunk wholly past the last column of a partial tile
   const int n_peers = to_peers ? ep.n_peers : 0;
   const float alpha = g * ep.s2;
@@ -148,9 +155,9 @@ __device__ __forceinline__ void gemm_store_chunk32(const uint32_t (&r)[32], int 
         }
       }
       uint2 packed;
-      const uint32_t sb = quantize_block<kEngine>(v, __ldg(ep.q_g), false, packed);
-      *reinterpret_cast<uint2 *>(ep.q_codes + static_cast<size_t>(row) * (n >> 2) + (col0 >> 2)) = packed;
-      ep.q_scales[tiled_scale_offset(row, col0 >> 5, ep.q_slots)] = static_cast<uint8_t>(sb);
+      const uint32_t sb = quantize_block<kEngine>(v, q_g, false, packed);
+      *reinterpret_cast<uint2 *>(ep.q_codes + static_cast<size_t>(row) * ep.q_ld + (col0 >> 2)) = packed;
+      ep.q_scales[tiled_scale_offset(row, ep.q_slot0 + (col0 >> 5), ep.q_slots)] = static_cast<uint8_t>(sb);
       return;
     }
     __nv_bfloat16 * dst = c + static_cast<size_t>(row) * ldc + (col0 >> 1);

@@ -31,9 +31,14 @@
 namespace q35b {
 namespace {
 
+#ifndef Q35B_TILE_N
+#define Q35B_TILE_N 192
+#endif
 constexpr int kCtaRows = 128;            // rows of A staged per CTA
 constexpr int kTileM = 256;              // output tile of the pair: 256 tokens ...
-constexpr int kTileN = 192;              // ... by 192 weight rows
+constexpr int kTileN = Q35B_TILE_N;      // ... by 192 (two accumulators in TMEM) or 256 (one) weight rows
+static_assert(kTileN == 192 || kTileN == 256, "tile width");
+constexpr int kAccs = kTileN == 192 ? 2 : 1;  // accumulators that fit beside the scale factors in 512 TMEM columns
 constexpr int kCtaBRows = kTileN / 2;    // rows of B staged per CTA
 constexpr int kStepBytes = 128;          // 256 FP4 columns
 constexpr int kMmaPerStage = 4;
@@ -43,16 +48,20 @@ constexpr int kBBytes = kCtaBRows * kStepBytes;
 constexpr int kSfaBytes = kMmaPerStage * kSfChunk;
 constexpr int kSfbBytes = 2 * kMmaPerStage * kSfChunk;
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 34816
-constexpr int kStages = 6;
+#ifndef Q35B_STAGES
+#define Q35B_STAGES (Q35B_TILE_N == 192 ? 6 : 5)
+#endif
+constexpr int kStages = Q35B_STAGES;
 #ifndef Q35B_EPI_WARPS
-#define Q35B_EPI_WARPS 12
+#define Q35B_EPI_WARPS (Q35B_TILE_N == 192 ? 12 : 16)
 #endif
 constexpr int kEpilogueWarps = Q35B_EPI_WARPS;  // kEpilogueWarps / 4 per TMEM lane quarter, each a column slice
 constexpr int kThreads = (2 + kEpilogueWarps) * 32;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 constexpr int kEpiCols = kTileN / (kEpilogueWarps / 4);  // columns drained by one epilogue warp
 static_assert(kEpilogueWarps % 4 == 0 && kEpiCols % 32 == 0 && kEpiCols * (kEpilogueWarps / 4) == kTileN, "epilogue column split");
-constexpr int kAccCols = 2 * kTileN;     // two accumulators
+static_assert(kStages * kStageBytes + 1024 + 256 <= 227 * 1024, "shared memory");
+constexpr int kAccCols = kAccs * kTileN;
 constexpr int kSfaCols = kMmaPerStage * 4;
 constexpr int kSfbCols = kMmaPerStage * 8;
 constexpr int kTmemCols = 512;
@@ -269,9 +278,9 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t li = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
-        const uint32_t ab = li & 1;
-        if (!mbar_wait(smem_u32(drained + ab), ((li >> 1) & 1) ^ 1) ||
-            !mbar_wait(smem_u32(peer_drained + ab), ((li >> 1) & 1) ^ 1)) {
+        const uint32_t ab = li % kAccs;
+        const uint32_t acc_phase = (li / kAccs) & 1;
+        if (!mbar_wait(smem_u32(drained + ab), acc_phase ^ 1) || !mbar_wait(smem_u32(peer_drained + ab), acc_phase ^ 1)) {
           atomicExch(status, kMmaDrainWait);
           ok = false;
           break;
@@ -320,8 +329,8 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // read an accumulator out, so that none of them spends a cluster round trip on it ----------------
       uint32_t li = 0;
       for (int tile = pair; tile < num_tiles; tile += num_pairs, ++li) {
-        const uint32_t ab = li & 1;
-        if (!mbar_wait(smem_u32(drained + ab), (li >> 1) & 1)) {
+        const uint32_t ab = li % kAccs;
+        if (!mbar_wait(smem_u32(drained + ab), (li / kAccs) & 1)) {
           atomicExch(status, kEpilogueWait);
           break;
         }
@@ -333,13 +342,14 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int quarter = warp & 3;                 // TMEM lanes 32 * quarter .. + 31 (fixed by the warp's index)
     const int col_base = ((warp - 2) >> 2) * kEpiCols;
     const float g = __ldg(g_dev);
+    const float q_g = ep.q_g != nullptr ? __ldg(ep.q_g) : 1.0f;
     uint32_t li = 0;
     bool ok = !aborted;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++li) {
       const int tm = tile % m_tiles;
       const int tn = tile / m_tiles;
-      const uint32_t ab = li & 1;
-      if (!mbar_wait(smem_u32(tmem_full + ab), (li >> 1) & 1)) {
+      const uint32_t ab = li % kAccs;
+      if (!mbar_wait(smem_u32(tmem_full + ab), (li / kAccs) & 1)) {
         if (lane == 0) atomicExch(status, kEpilogueWait);
         ok = false;
         break;
@@ -361,7 +371,7 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       if (row < m) {
 #pragma unroll
         for (int j = 0; j < kEpiCols / 32; ++j) {
-          gemm_store_chunk32(r[j], row, tn * kTileN + col_base + 32 * j, n, g, ep, c, ldc, !forward);
+          gemm_store_chunk32(r[j], row, tn * kTileN + col_base + 32 * j, n, g, ep, c, ldc, !forward, q_g);
         }
       }
       if (forward) {

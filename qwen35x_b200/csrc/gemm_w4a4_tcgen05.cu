@@ -313,13 +313,14 @@ gemm_w4a4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float g = __ldg(g_dev);
+      const float q_g = ep.q_g != nullptr ? __ldg(ep.q_g) : 1.0f;
       const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < m) gemm_store_chunk32(r, row, tile_n * BLOCK_N + c0, n, g, ep, c, ldc);
+        if (row < m) gemm_store_chunk32(r, row, tile_n * BLOCK_N + c0, n, g, ep, c, ldc, true, q_g);
       }
     }
   }
@@ -448,6 +449,9 @@ int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8
       return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection received a null device buffer.");
     }
     if ((out_cols % 64) != 0) return fail(Q35B_ERR_SHAPE, "NVFP4 output of the prefill projection needs rows / 2 to be a multiple of 64.");
+    if ((w->row_begin % 128) != 0 || qout->total_cols < w->row_begin / 2 + out_cols || (qout->total_cols % 64) != 0) {
+      return fail(Q35B_ERR_SHAPE, "NVFP4 output of the prefill projection: the shard's columns do not fit the given width.");
+    }
     if ((reinterpret_cast<uintptr_t>(qout->codes) & 7u) != 0) {
       return fail(Q35B_ERR_ARGUMENT, "NVFP4 prefill projection buffers must be 16-byte aligned.");
     }
@@ -462,10 +466,12 @@ int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8
   ep.residual = static_cast<const __nv_bfloat16 *>(residual_bf16);
   ep.ldr = ldr;
   if (qout != nullptr) {
-    ep.q_codes = qout->codes;
+    ep.q_codes = qout->codes + w->row_begin / 4;   // two output columns per byte, two weight rows per output column
     ep.q_scales = qout->scales_tiled;
     ep.q_g = qout->g_dev;
-    ep.q_slots = round_up_int(out_cols / 16, 4);
+    ep.q_slots = round_up_int(qout->total_cols / 16, 4);
+    ep.q_ld = qout->total_cols / 2;
+    ep.q_slot0 = w->row_begin / 32;
   }
   if (gather != nullptr) {
     static_assert(sizeof(gather->peer_c) / sizeof(gather->peer_c[0]) == GemmEpilogue::kMaxPeers, "peer table size");

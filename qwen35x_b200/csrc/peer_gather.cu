@@ -11,6 +11,7 @@
 // No TMA and no multicast touch peer memory: only st.global from the epilogue warps and one flag word per peer.
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstring>
 
 #include "engine.h"
@@ -49,6 +50,68 @@ __global__ void peer_gather_wait_kernel(const unsigned int * flags, int world, i
     __nanosleep(64);
   }
   atomicExch(status, kStatusGatherWait);
+}
+
+// Copies up to four 2-D byte regions of this rank's buffer to the same place in every other rank's buffer and
+// then signals the epoch, with the protocol of the gathering GEMM (system-wide fence, CTA count, last CTA writes
+// this rank's flag slot on every peer).  A thread moves 16-byte pieces: it reads one from local memory and stores
+// it to each peer, so a warp's store instruction covers 512 contiguous bytes of one peer (whole 128-byte lines,
+// the unit NVLink moves well).  Used where the producer kernel writes pieces too small to forward itself: the
+// NVFP4 codes (8 bytes per row per thread) and scale bytes of the gate/up epilogue, and narrow BF16 shards.
+struct PushRegion {
+  unsigned long long offset;    // of the region's first byte inside the buffer
+  unsigned long long ld;        // bytes between rows
+  unsigned int row_pieces;      // 16-byte pieces per row
+  unsigned int rows;
+};
+struct PushArgs {
+  PushRegion region[4];
+  int n_regions;
+  int n_peers;
+  uint8_t * local;
+  uint8_t * peer[GemmEpilogue::kMaxPeers];
+  unsigned int * peer_flag[GemmEpilogue::kMaxPeers];
+  unsigned int * done_counter;
+  unsigned int epoch;
+};
+
+__global__ void __launch_bounds__(256) peer_push_kernel(const PushArgs a) {
+  constexpr int kUnroll = 4;
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+  for (int ri = 0; ri < a.n_regions; ++ri) {
+    const PushRegion rg = a.region[ri];
+    const unsigned long long pieces = static_cast<unsigned long long>(rg.rows) * rg.row_pieces;
+    for (unsigned long long i0 = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < pieces;
+         i0 += stride * kUnroll) {
+      uint4 v[kUnroll];
+      unsigned long long off[kUnroll];
+      // loads first, then the stores: the stores of one piece never hold back the load of the next
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const unsigned long long i = i0 + u * stride;
+        if (i < pieces) {
+          off[u] = rg.offset + (i / rg.row_pieces) * rg.ld + (i % rg.row_pieces) * 16ull;
+          v[u] = __ldcg(reinterpret_cast<const uint4 *>(a.local + off[u]));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (i0 + u * stride < pieces) {
+#pragma unroll
+          for (int p = 0; p < GemmEpilogue::kMaxPeers; ++p) {
+            if (p < a.n_peers) *reinterpret_cast<uint4 *>(a.peer[p] + off[u]) = v[u];
+          }
+        }
+      }
+    }
+  }
+  GemmEpilogue ep;
+  ep.n_peers = a.n_peers;
+#pragma unroll
+  for (int p = 0; p < GemmEpilogue::kMaxPeers; ++p) ep.peer_flag[p] = a.peer_flag[p];
+  ep.done_counter = a.done_counter;
+  ep.epoch = a.epoch;
+  gemm_signal_peers(ep, true);
 }
 
 // A rank whose shard is empty (more ranks than 128-row blocks) computes nothing but still has to tell the others
@@ -173,5 +236,52 @@ int q35b_peer_gather_wait(q35b_peer_buffer * const * buffers, int world, int ran
                                                                          status_dev);
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "peer_gather_wait_kernel launch");
+  return Q35B_OK;
+}
+
+int q35b_peer_push(q35b_peer_buffer * const * buffers, int world, int rank, const q35b_peer_region * regions, int n_regions,
+                   unsigned int epoch, q35b_stream stream) {
+  if (buffers == nullptr || world < 1 || world > kMaxRanks || rank < 0 || rank >= world || buffers[rank] == nullptr ||
+      regions == nullptr || n_regions < 1 || n_regions > 4) {
+    return fail(Q35B_ERR_ARGUMENT, "Invalid rank layout or region list for the peer push.");
+  }
+  PushArgs a = {};
+  unsigned long long pieces = 0;
+  for (int i = 0; i < n_regions; ++i) {
+    const q35b_peer_region & r = regions[i];
+    if (r.rows < 0 || (r.offset % 16) != 0 || (r.row_bytes % 16) != 0 || (r.ld_bytes % 16) != 0 || r.ld_bytes < r.row_bytes) {
+      return fail(Q35B_ERR_ARGUMENT, "Peer push regions need 16-byte aligned offsets, row sizes and row strides.");
+    }
+    const size_t end = r.rows > 0 ? r.offset + static_cast<size_t>(r.rows - 1) * r.ld_bytes + r.row_bytes : r.offset;
+    for (int q = 0; q < world; ++q) {
+      if (buffers[q] == nullptr || buffers[q]->base == nullptr || buffers[q]->data_bytes < end) {
+        return fail(Q35B_ERR_ARGUMENT, "A peer buffer of the push is missing or too small for a region.");
+      }
+    }
+    a.region[i].offset = r.offset;
+    a.region[i].ld = r.ld_bytes;
+    a.region[i].row_pieces = static_cast<unsigned int>(r.row_bytes / 16);
+    a.region[i].rows = static_cast<unsigned int>(r.rows);
+    pieces += static_cast<unsigned long long>(r.rows) * (r.row_bytes / 16);
+  }
+  a.n_regions = n_regions;
+  a.local = buffers[rank]->base;
+  for (int q = 0; q < world; ++q) {
+    if (q == rank) continue;
+    a.peer[a.n_peers] = buffers[q]->base;
+    a.peer_flag[a.n_peers] = flag_words(buffers[q]) + rank;
+    ++a.n_peers;
+  }
+  a.done_counter = flag_words(buffers[rank]) + kMaxRanks;
+  a.epoch = epoch;
+  if (world == 1) return Q35B_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Q35B_CUDA_TRY(cudaMemsetAsync(a.done_counter, 0, sizeof(unsigned int), s), "cudaMemsetAsync(push counter)");
+  // enough threads to keep every NVLink busy, few enough that the closing count stays cheap
+  const unsigned long long want = (pieces + 256ull * 4 - 1) / (256ull * 4);
+  const int blocks = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(want, 2ull * sm_count())));
+  peer_push_kernel<<<blocks, 256, 0, s>>>(a);
+  count_launch();
+  Q35B_CUDA_TRY(cudaGetLastError(), "peer_push_kernel launch");
   return Q35B_OK;
 }

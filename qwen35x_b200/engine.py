@@ -23,6 +23,10 @@ class Q35bError(RuntimeError):
         self.status = status
 
 
+class _PeerRegion(C.Structure):
+    _fields_ = [("offset", C.c_size_t), ("row_bytes", C.c_size_t), ("ld_bytes", C.c_size_t), ("rows", C.c_int)]
+
+
 def lib() -> C.CDLL:
     """Load libq35b.so (built by `python -m qwen35x_b200.build`); raises if it is missing."""
     global _lib
@@ -41,6 +45,8 @@ def lib() -> C.CDLL:
     L.q35b_weight_create_from_device.argtypes = [vp, vp, f, f, i, i, i, i, vp, C.POINTER(vp)]
     L.q35b_weight_create_gate_up.restype = i
     L.q35b_weight_create_gate_up.argtypes = [vp, vp, f, vp, vp, f, i, i, C.POINTER(vp)]
+    L.q35b_weight_create_gate_up_shard.restype = i
+    L.q35b_weight_create_gate_up_shard.argtypes = [vp, vp, f, vp, vp, f, i, i, i, i, C.POINTER(vp)]
     L.q35b_weight_is_gate_up.restype = i
     L.q35b_weight_is_gate_up.argtypes = [vp]
     L.q35b_weight_dequant_bf16.restype = i
@@ -112,6 +118,8 @@ def lib() -> C.CDLL:
     L.q35b_gemm_w4a4_bf16_allgather.argtypes = [vp, vp, vp, vp, i, C.POINTER(vp), i, i, i, C.c_uint, vp, vp]
     L.q35b_peer_gather_wait.restype = i
     L.q35b_peer_gather_wait.argtypes = [C.POINTER(vp), i, i, C.c_uint, vp, vp]
+    L.q35b_peer_push.restype = i
+    L.q35b_peer_push.argtypes = [C.POINTER(vp), i, i, C.POINTER(_PeerRegion), i, C.c_uint, vp]
     L.q35b_gemm_w4a4_gate_up_nvfp4.restype = i
     L.q35b_gemm_w4a4_gate_up_nvfp4.argtypes = [vp, vp, vp, vp, i, vp, vp, vp, vp, vp]
     L.q35b_debug_encode_ue4m3.restype = C.c_uint8
@@ -185,16 +193,19 @@ class Nvfp4Weight:
         return cls(h.value, n, k, weight_scale_2, input_scale)
 
     @classmethod
-    def gate_up_from_host(cls, gate_codes, gate_scales, gate_s2: float, up_codes, up_scales, up_s2: float) -> "Nvfp4Weight":
-        """gate_proj + up_proj as one weight with rows alternating in groups of eight (for the fused SiLU epilogue)."""
+    def gate_up_from_host(cls, gate_codes, gate_scales, gate_s2: float, up_codes, up_scales, up_s2: float,
+                          shard_index: int = 0, shard_count: int = 1) -> "Nvfp4Weight":
+        """gate_proj + up_proj as one weight with rows alternating in groups of eight (for the fused SiLU epilogue);
+        with shard_count > 1 the row shard `shard_index` of that interleaved matrix."""
         _torch()
         arrs = [np.ascontiguousarray(a, dtype=np.uint8) for a in (gate_codes, gate_scales, up_codes, up_scales)]
         n_half, k = arrs[0].shape[0], arrs[0].shape[1] * 2
         if arrs[2].shape != arrs[0].shape or arrs[1].shape != (n_half, k // 16) or arrs[3].shape != (n_half, k // 16):
             raise Q35bError(2, "NVFP4 packed weight or scale size does not match matrix dimensions.")
         h = C.c_void_p()
-        _check(lib().q35b_weight_create_gate_up(arrs[0].ctypes.data, arrs[1].ctypes.data, gate_s2, arrs[2].ctypes.data,
-                                                arrs[3].ctypes.data, up_s2, n_half, k, C.byref(h)))
+        _check(lib().q35b_weight_create_gate_up_shard(arrs[0].ctypes.data, arrs[1].ctypes.data, gate_s2, arrs[2].ctypes.data,
+                                                      arrs[3].ctypes.data, up_s2, n_half, k, shard_index, shard_count,
+                                                      C.byref(h)))
         return cls(h.value, 2 * n_half, k, gate_s2, 1.0)
 
     def dequant_bf16(self):
@@ -408,11 +419,12 @@ def gemm_w4a4(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, out=None,
 
 def gemm_w4a4_gate_up_quant(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int, out_scale, scratch=None, status=None):
     """Gate/up prefill projection whose epilogue quantises silu(gate) * up to NVFP4 with the given per-tensor scale
-    (`out_scale`: 1-element fp32 device tensor) -> (codes [m, rows/4] uint8, tiled scales, out_scale), the A operand
-    of the down projection's gemm_w4a4.  `scratch` = act_scratch(m, rows // 2, device) to reuse buffers."""
+    (`out_scale`: 1-element fp32 device tensor) -> (codes [m, n_half/2] uint8, tiled scales, out_scale), the A operand
+    of the down projection's gemm_w4a4.  `scratch` = act_scratch(m, n_half, device) to reuse buffers; a row shard of
+    the gate/up weight writes only its own columns of that whole-width activation."""
     torch = _torch()
     assert weight.gate_up and out_scale.dtype == torch.float32 and out_scale.is_cuda
-    inter = weight.rows // 2
+    inter = weight.n_total // 2
     codes, scales, _ = scratch if scratch is not None else act_scratch(m, inter, a_codes.device)
     st = status.data_ptr() if status is not None else None
     _check(lib().q35b_gemm_w4a4_gate_up_nvfp4(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(), g.data_ptr(), m,
@@ -436,6 +448,21 @@ class PeerBuffer:
         h = C.c_void_p()
         _check(lib().q35b_peer_buffer_create(m * n * 2, C.byref(h)))
         return cls(h, m, n, torch.device("cuda", torch.cuda.current_device()))
+
+    @classmethod
+    def create_bytes(cls, nbytes: int) -> "PeerBuffer":
+        """A buffer of raw bytes (several regions of different kinds, see peer_push); `tensor()` views it as
+        [1, nbytes / 2] BF16, `bytes()` as uint8."""
+        assert nbytes % 2 == 0
+        return cls.create(1, nbytes // 2)
+
+    @classmethod
+    def open_bytes(cls, handle: bytes, nbytes: int) -> "PeerBuffer":
+        return cls.open(handle, 1, nbytes // 2)
+
+    def bytes(self):
+        torch = _torch()
+        return self.tensor().view(torch.uint8).reshape(-1)
 
     @classmethod
     def open(cls, handle: bytes, m: int, n: int) -> "PeerBuffer":
@@ -488,6 +515,16 @@ def gemm_w4a4_allgather(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: int,
                                                arr, world, rank, buffers[rank].n, epoch, status.data_ptr(), _stream_ptr(torch)))
     if wait:
         peer_gather_wait(buffers, rank, epoch, status)
+
+
+def peer_push(buffers, rank: int, regions, epoch: int) -> None:
+    """Copy regions [(offset, rows, row_bytes, ld_bytes)] of buffers[rank] to the same place in every other rank's
+    buffer and signal `epoch` (q35b_peer_push); the receivers wait with peer_gather_wait(.., epoch, ..)."""
+    torch = _torch()
+    world = len(buffers)
+    arr = (C.c_void_p * world)(*[b.handle for b in buffers])
+    regs = (_PeerRegion * len(regions))(*[_PeerRegion(o, rb, ld, r) for (o, r, rb, ld) in regions])
+    _check(lib().q35b_peer_push(arr, world, rank, regs, len(regions), epoch, _stream_ptr(torch)))
 
 
 def peer_gather_wait(buffers, rank: int, epoch: int, status) -> None:

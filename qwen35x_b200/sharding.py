@@ -135,3 +135,95 @@ class PeerGather:
         code = int(self.status.item())
         if code != 0:
             raise RuntimeError(f"device-side wait expired in the gathering projection, code {code}")
+
+
+def _round_up(v: int, m: int) -> int:
+    return (v + m - 1) // m * m
+
+
+class MlpLayout:
+    """Byte layout of one rank's peer buffer for the N-sharded prefill MLP block (hidden -> intermediate -> hidden):
+
+        [h codes  m x inter/2][h tiled scales  ceil128(m) x ceil4(inter/16)][out  m x hidden BF16]
+
+    h = silu(gate x) * up x as an NVFP4 activation, written shard by shard: rank r's gate/up GEMM fills its own
+    columns locally, `push` regions carry them to the other ranks.  Pure arithmetic, no GPU needed."""
+
+    def __init__(self, m: int, hidden: int, inter: int):
+        assert inter % 64 == 0 and hidden % 8 == 0
+        self.m, self.hidden, self.inter = m, hidden, inter
+        self.codes_off = 0
+        self.codes_ld = inter // 2
+        self.scales_off = _round_up(m * self.codes_ld, 256)
+        self.scale_slots = _round_up(inter // 16, 4)
+        self.row_blocks = _round_up(m, 128) // 128
+        self.scales_bytes = self.row_blocks * 128 * self.scale_slots
+        self.out_off = _round_up(self.scales_off + self.scales_bytes, 256)
+        self.out_ld = hidden * 2
+        self.total = _round_up(self.out_off + m * self.out_ld, 256)
+
+    def h_regions(self, col0: int, cols: int):
+        """Regions (offset, rows, row_bytes, ld_bytes) holding columns [col0, col0 + cols) of h: the code bytes of
+        every row, and per 128-row block the run of 512-byte scale tiles of those columns."""
+        assert col0 % 64 == 0 and cols % 64 == 0
+        if cols == 0:
+            return []
+        return [(self.codes_off + col0 // 2, self.m, cols // 2, self.codes_ld),
+                (self.scales_off + (col0 // 64) * 512, self.row_blocks, (cols // 64) * 512, (self.scale_slots // 4) * 512)]
+
+    def out_regions(self, col0: int, cols: int):
+        assert col0 % 8 == 0 and cols % 8 == 0
+        return [(self.out_off + col0 * 2, self.m, cols * 2, self.out_ld)] if cols else []
+
+
+class PeerMlp:
+    """One N-sharded prefill MLP block per call, out = down(silu(gate x) * up x) + residual on every rank:
+
+        quantise x (replicated)  ->  gate/up GEMM on this rank's shard, epilogue writes NVFP4 h columns
+        ->  push h columns to all ranks, wait  ->  down GEMM on this rank's row shard (+ residual)
+        ->  push the BF16 output columns to all ranks, wait.
+
+    The exchange moves 0.5625 bytes per element of h and 2 bytes per element of the output instead of the BF16
+    all-gather of gate/up (4 bytes per element of h).  `buffers` lists every rank's PeerBuffer (buffers[rank] local);
+    in one process all of them can be local (emulated ranks: call `stage(i)` for all ranks in turn)."""
+
+    def __init__(self, layout: MlpLayout, buffers, rank: int, gate_up_shard, down_shard, h_scale, status):
+        self.layout, self.buffers, self.rank = layout, buffers, rank
+        self.gate_up, self.down, self.h_scale, self.status = gate_up_shard, down_shard, h_scale, status
+        self.world = len(buffers)
+        self.epoch = 0
+        raw = buffers[rank].bytes()
+        L = layout
+        self.h_codes = raw[L.codes_off:L.codes_off + L.m * L.codes_ld]
+        self.h_scales = raw[L.scales_off:L.scales_off + L.scales_bytes]
+        self.out = buffers[rank].tensor().reshape(-1)[L.out_off // 2:L.out_off // 2 + L.m * L.hidden].view(L.m, L.hidden)
+
+    def stage(self, i: int, a_codes=None, a_scales=None, g=None, residual=None):
+        """Stage 0: gate/up GEMM + push of h; 1: wait for h; 2: down GEMM + push of the output; 3: wait for it."""
+        from . import engine
+
+        L = self.layout
+        if i == 0:
+            self.epoch += 2
+            engine.gemm_w4a4_gate_up_quant(self.gate_up, a_codes, a_scales, g, L.m, self.h_scale,
+                                           scratch=(self.h_codes, self.h_scales, None), status=self.status)
+            regs = L.h_regions(self.gate_up.row_begin // 2, self.gate_up.rows // 2)
+            engine.peer_push(self.buffers, self.rank, regs or [(0, 0, 16, 16)], self.epoch - 1)
+        elif i == 1:
+            engine.peer_gather_wait(self.buffers, self.rank, self.epoch - 1, self.status)
+        elif i == 2:
+            col0, cols = self.down.row_begin, self.down.rows
+            if cols:
+                res = residual[:, col0:col0 + cols] if residual is not None else None
+                engine.gemm_w4a4(self.down, self.h_codes.view(L.m, L.codes_ld), self.h_scales, self.h_scale, L.m,
+                                 out=self.out[:, col0:col0 + cols], status=self.status, residual=res)
+            engine.peer_push(self.buffers, self.rank, L.out_regions(col0, cols) or [(0, 0, 16, 16)], self.epoch)
+        else:
+            engine.peer_gather_wait(self.buffers, self.rank, self.epoch, self.status)
+
+    def run(self, a_codes, a_scales, g, residual=None):
+        self.stage(0, a_codes, a_scales, g)
+        self.stage(1)
+        self.stage(2, residual=residual)
+        self.stage(3)
+        return self.out

@@ -22,15 +22,20 @@ def test_single_process(oracle):
     assert r.returncode == 0, r.stderr[-2000:]
     (line,) = _lines(r.stdout)
     assert KEYS <= set(line) and line["impl"] == "reference" and line["metric"] == "nvfp4_decode_step_bandwidth"
-    assert line["value"] > 0 and line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] == "port"
+    assert line["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    assert "unavailable" in line["reference_gpu"] or "decode_step_scale_group" in line["reference_gpu"]
     assert line["e2e"]["value"] == line["value"] and line["e2e"]["h2d_bytes_per_step"] == 0
 
 
 def test_two_ranks_only_rank_zero_reports(oracle):
-    env = dict(os.environ, OMP_NUM_THREADS="2")
+    # torch.distributed.run sets OMP_NUM_THREADS=1 for its workers: the arm must not take its thread count from there
+    env = dict(os.environ)
+    env.pop("OMP_NUM_THREADS", None)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29641", str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=ROOT, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     lines = _lines(r.stdout)
     assert len(lines) == 1 and lines[0]["impl"] == "reference" and lines[0]["n_gpus"] == 2
+    assert lines[0]["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))

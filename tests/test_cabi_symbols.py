@@ -63,7 +63,7 @@ def test_no_cpu_fallback(engine):
 
 def test_shape_report_renders_markdown():
     """The per-shape report's table renderer (no GPU): every section of a report dict appears with its rows."""
-    from qwen35x_b200 import shape_report
+    import shape_report
 
     gemm = {"us": 10.0, "TFLOP/s": 100.0, "fp4_nominal_frac": 0.011, "frac_of_4x_measured_bf16": 0.015}
     report = {

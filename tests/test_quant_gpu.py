@@ -117,12 +117,15 @@ def test_full_size_round_trip_property(engine, oracle):
     assert same > 0.9
 
 
-def test_division_at_every_rounding_boundary(engine, oracle):
-    """The block quantiser divides sixteen values by one shared divisor with a reciprocal-and-correct sequence
-    instead of sixteen IEEE divisions.  Values are placed -3..+3 ulp around d times every E2M1 rounding boundary
-    (0.25 .. 5.0), for thousands of divisors d spread over 60 binary orders of magnitude (so that both the
-    shared-reciprocal path and the plain-division path for extreme exponents run): codes must equal the oracle's,
-    which divides with the host's IEEE division."""
+@pytest.mark.parametrize("spread", [3, 24])
+def test_division_at_every_rounding_boundary(engine, oracle, spread):
+    """The block quantiser does not run sixteen IEEE divisions and sixteen threshold scans: it multiplies by a shared
+    refined reciprocal and hands the products to the hardware E2M1 converter unless one of them lies within 8 ulp of
+    a rounding boundary, in which case the block is redone with correctly rounded quotients and the ties-down
+    encoder.  Values are placed -spread..+spread ulp around d times every E2M1 rounding boundary (0.25 .. 5.0) - 3
+    keeps every probe on the exact path, 24 straddles the hand-over between the two - for thousands of divisors d
+    spread over 60 binary orders of magnitude (so that the plain-division path for extreme exponents runs as well):
+    codes must equal the oracle's, which divides with the host's IEEE division."""
     import torch
 
     rng = np.random.default_rng(77)
@@ -139,7 +142,7 @@ def test_division_at_every_rounding_boundary(engine, oracle):
         d = (np.maximum(e4[scales0], np.float32(1e-8)) * np.float32(g)).astype(np.float32)  # [n, k/16]
         for j in range(1, 16):
             target = (bounds[rng.integers(0, 7, size=d.shape)] * d).astype(np.float32)
-            bits = target.view(np.int32) + rng.integers(-3, 4, size=d.shape, dtype=np.int32)
+            bits = target.view(np.int32) + rng.integers(-spread, spread + 1, size=d.shape, dtype=np.int32)
             w[:, j::16] = bits.view(np.float32) * rng.choice(np.array([-1.0, 1.0], dtype=np.float32), size=d.shape)
         e_codes, e_scales, e_g = oracle.quantize_nvfp4(w)
         assert np.array_equal(e_scales, scales0) and e_g == g  # the probes did not move any amax
@@ -147,3 +150,22 @@ def test_division_at_every_rounding_boundary(engine, oracle):
         assert np.float32(s2).view(np.uint32) == np.float32(e_g).view(np.uint32)
         assert np.array_equal(scales.cpu().numpy(), e_scales)
         assert np.array_equal(codes.cpu().numpy(), e_codes), f"trial {trial}: {(codes.cpu().numpy() != e_codes).sum()} code bytes differ"
+
+
+def test_zeros_signed_zeros_and_values_that_round_to_zero(engine, oracle):
+    """Exact zeros and -0 encode as code 0; a negative value too small for the first level keeps its sign bit
+    (code 8), as (value < 0) does in the reference's encoder; blocks mixing them with ordinary values included."""
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((64, 1024)).astype(np.float32)
+    x[rng.random(x.shape) < 0.3] = 0.0
+    x[rng.random(x.shape) < 0.1] = -0.0
+    tiny = rng.random(x.shape) < 0.1
+    x[tiny] = (-1e-4 * rng.random(x.shape).astype(np.float32))[tiny]
+    x[5] = 0.0
+    x[6] = -0.0
+    xb = oracle.bf16_round(x)
+    codes, _, _ = _run(engine, oracle, xb)
+    assert (codes.cpu().numpy() & 0x08).any()  # some negative zeros were produced, and matched the oracle
+    _run(engine, oracle, xb, global_scale=2.0 ** -9)  # a power-of-two scale: many quotients land exactly on boundaries
+    q = (rng.integers(-24, 25, size=(32, 512)) * 0.25).astype(np.float32)  # multiples of 0.25: ties everywhere
+    _run(engine, oracle, oracle.bf16_round(q), global_scale=0.125)  # blocks holding a +-6 get the divisor 1.0
