@@ -46,6 +46,7 @@ GEMM_M = 4096
 GEMM_SETS = 5
 MLP_HIDDEN, MLP_INTER = 2560, 9216
 MLP_SETS = 3
+MLP_CHUNKS = 1  # token groups of the sharded MLP block (PeerMlp.run chunks): 2 and 4 measured slower on 2 GPUs (203, 275 us against 186)
 L2_BYTES = 126 * 1024 * 1024
 PEER_COPY_GBS = 770.0  # measured peer-copy rate per direction on this pool's NVLink (nominal 900)
 FP4_NOMINAL_TFLOPS = 9000.0
@@ -485,9 +486,24 @@ def bench_gemm(args, q, torch, dist, timer, device, rank, world, pk) -> dict | N
         ms_full = timer.per_call(st, full_step, steps, warm)
         ms_nccl = None
     else:
-        # every call carries a new epoch in its kernel arguments, so these run as eager launches
-        ms_full = timer.per_call(st, lambda: one(True, True), steps, warm)
-        ms_nccl = timer.per_call(st, lambda: one(True, True, fused=False), steps, warm)
+        if peer is not None:
+            # quantise + gathering GEMM + wait as one CUDA graph per set (epochs are counted on the device)
+            graphs = []
+            for i in range(GEMM_SETS):
+                timer.barrier()
+                graphs.append(capture(torch, st, lambda i=i: one(True, True, index=i)))
+                timer.barrier()
+            gi = [0]
+
+            def fused_step():
+                graphs[gi[0] % GEMM_SETS].replay()
+                gi[0] += 1
+            ms_full = timer.per_call(st, fused_step, steps, warm)
+        else:
+            ms_full = None
+        ms_nccl = timer.per_call(st, lambda: one(True, True, fused=False), steps, warm)  # eager: NCCL launches
+        if ms_full is None:
+            ms_full = ms_nccl
     if peer is not None:
         try:
             peer.check()
@@ -707,19 +723,23 @@ def bench_mlp(args, q, torch, dist, timer, device, rank, world) -> dict:
         buffers = [local if r == rank else q.PeerBuffer.open_bytes(handles[r].tobytes(), layout.total) for r in range(world)]
         dist.barrier()
         runners = [sharding.PeerMlp(layout, buffers, rank, d["gu"], d["down"], h_scale, status) for d in data]
-        epoch = [0]
         gi = [0]
 
         def block(i):
-            d, p = data[i], runners[i]
-            p.epoch = epoch[0]  # the runners share one buffer: one epoch sequence
+            d = data[i]
             codes, scales, g = q.quantize_activations(d["x"], scratch=d["sx"])
-            y = p.run(codes, scales, g, residual=d["res"])
-            epoch[0] = p.epoch
-            return y
+            return runners[i].run(codes, scales, g, residual=d["res"], chunks=MLP_CHUNKS)
+
+        # one CUDA graph per set (the epochs of pushes and waits are counted on the device, so replays line up across
+        # ranks); captured between barriers, since the capture's warm-up run already exchanges data
+        graphs = []
+        for i in range(MLP_SETS):
+            timer.barrier()
+            graphs.append(capture(torch, st, lambda i=i: block(i)))
+            timer.barrier()
 
         def one():
-            block(gi[0] % MLP_SETS)
+            graphs[gi[0] % MLP_SETS].replay()
             gi[0] += 1
         ms = timer.per_call(st, one, steps, 3)
         with torch.cuda.stream(st):
@@ -731,7 +751,7 @@ def bench_mlp(args, q, torch, dist, timer, device, rank, world) -> dict:
             ok = bool(int(okt.item()))
             timer.barrier()
         exchange = ("NVFP4 intermediate columns and BF16 output columns pushed to every rank with peer-memory stores "
-                    "(q35b_peer_push) + flag waits; eager launches")
+                    f"(q35b_peer_push) + flag waits; one CUDA graph per block")
     h_bytes = m * inter * 9 // 16
     out_bytes = m * hidden * 2
     return {"workload": f"prefill MLP block M={m}, hidden {hidden}, intermediate {inter}, N-sharded over {world} GPU(s): "

@@ -111,6 +111,7 @@ struct GemmGather {
   unsigned int * peer_flag[7] = {};
   unsigned int * done_counter = nullptr;
   unsigned int epoch = 0;
+  unsigned int * send_seq = nullptr;   // used when epoch == 0 (see GemmEpilogue)
 };
 // Encodes the weight's tensor maps (host only, no device work); called by q35b_weight_create*.
 int build_weight_maps(q35b_weight * w);

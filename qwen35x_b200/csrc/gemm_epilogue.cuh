@@ -50,6 +50,10 @@ struct GemmEpilogue {
   unsigned int * peer_flag[kMaxPeers] = {};
   unsigned int * done_counter = nullptr;   // this rank's, zero between launches
   unsigned int epoch = 0;
+  // epoch == 0: the epoch is this rank's own send count, kept in device memory (send_seq) and advanced by the
+  // launch itself, so that a captured launch can be replayed: replay k signals k where the receivers' k-th wait
+  // expects it.
+  unsigned int * send_seq = nullptr;
 };
 
 __device__ __forceinline__ void st_global_v8(void * p, const uint32_t (&v)[8]) {
@@ -112,8 +116,13 @@ __device__ __forceinline__ void gemm_signal_peers(const GemmEpilogue & ep, bool 
     if (prev == gridDim.x * gridDim.y * gridDim.z - 1) {  // every other CTA fenced its stores before it counted itself
       *ep.done_counter = 0u;
       __threadfence_system();
+      unsigned int epoch = ep.epoch;
+      if (epoch == 0u && ep.send_seq != nullptr) {
+        epoch = *ep.send_seq + 1u;  // only this thread of the whole grid gets here
+        *ep.send_seq = epoch;
+      }
       if (ran) {
-        _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < ep.n_peers) *reinterpret_cast<volatile unsigned int *>(ep.peer_flag[i]) = ep.epoch;
+        _Pragma("unroll") for (int i = 0; i < GemmEpilogue::kMaxPeers; ++i) if (i < ep.n_peers) *reinterpret_cast<volatile unsigned int *>(ep.peer_flag[i]) = epoch;
       }
     }
   }

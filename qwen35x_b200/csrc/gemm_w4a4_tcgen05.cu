@@ -483,6 +483,7 @@ int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8
     }
     ep.done_counter = gather->done_counter;
     ep.epoch = gather->epoch;
+    ep.send_seq = gather->send_seq;
     // whole-row forwarding moves aligned 32-byte pieces; any other geometry takes the per-lane peer stores
     bool aligned = (ldc % 16) == 0 && (out_cols % 16) == 0 && (reinterpret_cast<uintptr_t>(c_bf16) & 31u) == 0;
     for (int i = 0; i < gather->n_peers; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(gather->peer_c[i]) & 31u) == 0;

@@ -3,13 +3,17 @@
 //   q35b --check-nvfp4-tensor            [--nvfp4-sample-rows N]
 //   q35b --bench-nvfp4-projection        [--nvfp4-projection-kernel row|warp|scale-group|blackwell-fp4|b200-simt|b200-stream]
 //   q35b --bench-nvfp4-prefill-projection [--nvfp4-prefill-seq-len S]
+//   q35b --probe-nvfp4-cublaslt          [--nvfp4-sample-rows N]      (the FP4 tensor-core probe; here tcgen05, not cuBLASLt)
 //        [--bench-warmup W] [--bench-iters K] (--synthetic ROWS,COLS[,SEED] | --hf-model-dir DIR [--nvfp4-tensor BASE])
+//   q35b --bench-nvfp4-gate-up [--bench-warmup W] [--bench-iters K]
+//        (--synthetic ROWS,COLS[,SEED] | --hf-model-dir DIR [--nvfp4-gate-tensor BASE] [--nvfp4-up-tensor BASE])
 //   q35b --validate-nvfp4-model --hf-model-dir DIR [--expect-layers N [--full-attention-interval I]]
 //
 // The tensor family comes from a ModelOpt NVFP4 checkpoint directory (--hf-model-dir/--nvfp4-tensor, as in the
 // reference, src/main.cpp:350-385) or from --synthetic (fp32 N(0, 0.02) weights quantised with the engine's NVFP4
 // recipe).  --validate-nvfp4-model applies the checkpoint rules without touching the GPU (src/main.cpp:560-591).
 // Output is the reference's `key: value` block.  Exit codes: 0 ok, 2 usage, 10 failure.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -23,16 +27,20 @@
 namespace rt = q35b::runtime;
 
 static void usage() {
-  std::cerr << "usage: q35b (--check-nvfp4-tensor | --bench-nvfp4-projection | --bench-nvfp4-prefill-projection)\n"
+  std::cerr << "usage: q35b (--check-nvfp4-tensor | --probe-nvfp4-cublaslt | --bench-nvfp4-projection |\n"
+               "             --bench-nvfp4-prefill-projection | --bench-nvfp4-gate-up)\n"
                "            (--synthetic ROWS,COLS[,SEED] | --hf-model-dir DIR [--nvfp4-tensor BASE])\n"
                "            [--nvfp4-projection-kernel NAME] [--nvfp4-sample-rows N]\n"
                "            [--nvfp4-prefill-seq-len S] [--bench-warmup W] [--bench-iters K] [--nvfp4-input-scale F]\n"
+               "            [--nvfp4-gate-tensor BASE] [--nvfp4-up-tensor BASE]\n"
                "       q35b --validate-nvfp4-model --hf-model-dir DIR [--expect-layers N [--full-attention-interval I]]\n";
 }
 
 int main(int argc, char ** argv) {
-  enum Mode { kNone, kCheck, kBench, kPrefill, kValidate } mode = kNone;
+  enum Mode { kNone, kCheck, kBench, kPrefill, kValidate, kGateUp, kProbe } mode = kNone;
   std::string model_dir, tensor_base;
+  // defaults of the reference's gate/up benchmark (include/qwen35x/runtime/runtime.h)
+  std::string gate_base = "model.language_model.layers.0.mlp.gate_proj", up_base = "model.language_model.layers.0.mlp.up_proj";
   int expect_layers = 0, full_interval = 4;
   bool input_scale_given = false;
   std::string kernel = "scale-group";
@@ -51,6 +59,10 @@ int main(int argc, char ** argv) {
     if (a == "--check-nvfp4-tensor") mode = kCheck;
     else if (a == "--bench-nvfp4-projection") mode = kBench;
     else if (a == "--bench-nvfp4-prefill-projection") mode = kPrefill;
+    else if (a == "--bench-nvfp4-gate-up") mode = kGateUp;
+    else if (a == "--probe-nvfp4-cublaslt") mode = kProbe;
+    else if (a == "--nvfp4-gate-tensor") gate_base = value("--nvfp4-gate-tensor");
+    else if (a == "--nvfp4-up-tensor") up_base = value("--nvfp4-up-tensor");
     else if (a == "--nvfp4-projection-kernel") kernel = value("--nvfp4-projection-kernel");
     else if (a == "--nvfp4-sample-rows") sample_rows = std::atoi(value("--nvfp4-sample-rows"));
     else if (a == "--nvfp4-prefill-seq-len") seq_len = std::atoi(value("--nvfp4-prefill-seq-len"));
@@ -109,6 +121,50 @@ int main(int argc, char ** argv) {
     return 2;
   }
 
+  if (mode == kGateUp) {
+    // two tensor families: gate_proj and up_proj of one MLP (src/main.cpp:760-790, src/runtime/runtime.cpp:280-360)
+    std::vector<std::uint8_t> g_packed, g_scales, u_packed, u_scales;
+    float g_s2 = 1.0f, u_s2 = 1.0f;
+    if (from_checkpoint) {
+      q35b::checkpoint::Nvfp4Tensor g, u;
+      if (!q35b::checkpoint::load_nvfp4_tensor(model_dir, gate_base, g, error) ||
+          !q35b::checkpoint::load_nvfp4_tensor(model_dir, up_base, u, error)) {
+        std::cerr << "NVFP4 gate/up benchmark failed: " << error << "\n";
+        return 10;
+      }
+      if (g.rows != u.rows || g.cols != u.cols) {
+        std::cerr << "NVFP4 gate/up benchmark failed: Gate and up packed weight shapes must match for benchmark.\n";
+        return 10;
+      }
+      g_packed = std::move(g.packed_weights); g_scales = std::move(g.weight_scales); g_s2 = g.weight_scale_2;
+      u_packed = std::move(u.packed_weights); u_scales = std::move(u.weight_scales); u_s2 = u.weight_scale_2;
+      rows = g.rows;
+      cols = g.cols;
+    } else {
+      if (!rt::make_synthetic_tensor(rows, cols, seed, 0.02f, g_packed, g_scales, g_s2, error) ||
+          !rt::make_synthetic_tensor(rows, cols, seed + 1, 0.02f, u_packed, u_scales, u_s2, error)) {
+        std::cerr << "NVFP4 synthetic tensor failed: " << error << "\n";
+        return 10;
+      }
+      gate_base = "synthetic[" + std::to_string(rows) + "," + std::to_string(cols) + "] seed " + std::to_string(seed);
+      up_base = "synthetic[" + std::to_string(rows) + "," + std::to_string(cols) + "] seed " + std::to_string(seed + 1);
+    }
+    double avg_ms = 0.0, max_abs_error = 0.0;
+    if (!rt::run_nvfp4_gate_up_benchmark(g_packed, g_scales, g_s2, u_packed, u_scales, u_s2, rows, cols, warmup, iters, avg_ms,
+                                         max_abs_error, error)) {
+      std::cerr << "NVFP4 gate/up benchmark failed: " << error << "\n";
+      return 10;
+    }
+    std::cout << "NVFP4 gate/up benchmark\n"
+              << "  gate_tensor_base: " << gate_base << "\n"
+              << "  up_tensor_base: " << up_base << "\n"
+              << "  source_shape: " << rows << "x" << cols << "\n"
+              << "  avg_iteration_ms: " << avg_ms << "\n"
+              << "  iterations_per_second: " << 1000.0 / avg_ms << "\n"
+              << "  max_abs_error: " << max_abs_error << "\n";
+    return 0;
+  }
+
   std::vector<std::uint8_t> packed, scales;
   float s2 = 1.0f;
   std::string tensor;
@@ -149,6 +205,26 @@ int main(int argc, char ** argv) {
               << "  packed_shape: [" << rows << ", " << cols / 2 << "]\n"
               << "  scale_shape: [" << rows << ", " << cols / 16 << "]\n"
               << "  sample_rows: " << sample_rows << "\n"
+              << "  max_abs_error: " << max_abs_error << "\n";
+    return 0;
+  }
+  if (mode == kProbe) {
+    double max_abs_error = 0.0, elapsed_ms = 0.0, max_abs_expected = 0.0, max_abs_actual = 0.0;
+    if (!rt::run_nvfp4_fp4_probe(packed, scales, s2, rows, cols, sample_rows, max_abs_error, elapsed_ms, max_abs_expected,
+                                 max_abs_actual, error)) {
+      std::cerr << "NVFP4 cuBLASLt probe failed: " << error << "\n";
+      return 10;
+    }
+    std::cout << "NVFP4 cuBLASLt probe\n"
+              << "  backend_note: sm_100a tcgen05 mxf4nvf4 block-scale path in place of cuBLASLt\n"
+              << "  tensor_base: " << tensor << "\n"
+              << "  source_shape: " << rows << "x" << cols << "\n"
+              << "  packed_shape: " << rows << "x" << cols / 2 << "\n"
+              << "  scale_shape: " << rows << "x" << cols / 16 << "\n"
+              << "  sample_rows: " << std::min(rows, std::max(1, sample_rows)) << "\n"
+              << "  elapsed_ms: " << elapsed_ms << "\n"
+              << "  max_abs_expected: " << max_abs_expected << "\n"
+              << "  max_abs_actual: " << max_abs_actual << "\n"
               << "  max_abs_error: " << max_abs_error << "\n";
     return 0;
   }

@@ -30,26 +30,40 @@ namespace q35b {
 namespace {
 
 constexpr int kMaxRanks = GemmEpilogue::kMaxPeers + 1;
-constexpr size_t kFlagBytes = 256;  // [kMaxRanks] epoch slots, then the owner's done counter
+constexpr size_t kFlagBytes = 256;  // [kMaxRanks] epoch slots, the owner's done counter, its send and wait counts
+constexpr int kSendSeqWord = kMaxRanks + 1;  // sends this rank has signalled with a self-counted epoch
+constexpr int kWaitSeqWord = kMaxRanks + 2;  // waits this rank has completed with a self-counted epoch
 constexpr uint32_t kGatherWaitLimit = 1u << 22;
 constexpr unsigned kStatusGatherWait = 31;
 
 inline unsigned int * flag_words(const q35b_peer_buffer * b) { return reinterpret_cast<unsigned int *>(b->base + b->flags_offset); }
 
-// One thread per rank: wait until that rank's slot carries this epoch (or a later one).
-__global__ void peer_gather_wait_kernel(const unsigned int * flags, int world, int rank, unsigned int epoch,
-                                        unsigned int * status) {
+// One thread per rank: wait until that rank's slot carries this epoch (or a later one).  epoch == 0: the epoch is
+// this rank's own count of such waits plus one (kept in the flag block, advanced here), which matches the senders'
+// self-counted epochs as long as every rank sends and waits the same number of times: a captured wait can be
+// replayed.
+__global__ void peer_gather_wait_kernel(unsigned int * flags, int world, int rank, unsigned int epoch,
+                                        unsigned int * status, uint32_t limit) {
   const int r = threadIdx.x;
-  if (r >= world || r == rank) return;
-  const volatile unsigned int * slot = flags + r;
-  for (uint32_t i = 0; i < kGatherWaitLimit; ++i) {
-    if (static_cast<int>(*slot - epoch) >= 0) {
-      __threadfence_system();  // the peer's matrix stores were fenced before its flag store
-      return;
+  __shared__ unsigned int expected;
+  if (r == 0) expected = epoch != 0u ? epoch : flags[kWaitSeqWord] + 1u;
+  __syncthreads();
+  const unsigned int want = expected;
+  if (r < world && r != rank) {
+    const volatile unsigned int * slot = flags + r;
+    bool seen = false;
+    for (uint32_t i = 0; i < limit; ++i) {
+      if (static_cast<int>(*slot - want) >= 0) {
+        __threadfence_system();  // the peer's matrix stores were fenced before its flag store
+        seen = true;
+        break;
+      }
+      __nanosleep(64);
     }
-    __nanosleep(64);
+    if (!seen) atomicExch(status, kStatusGatherWait);
   }
-  atomicExch(status, kStatusGatherWait);
+  __syncthreads();
+  if (r == 0 && epoch == 0u) flags[kWaitSeqWord] = want;
 }
 
 // Copies up to four 2-D byte regions of this rank's buffer to the same place in every other rank's buffer and
@@ -72,6 +86,7 @@ struct PushArgs {
   uint8_t * peer[GemmEpilogue::kMaxPeers];
   unsigned int * peer_flag[GemmEpilogue::kMaxPeers];
   unsigned int * done_counter;
+  unsigned int * send_seq;
   unsigned int epoch;
 };
 
@@ -111,13 +126,23 @@ __global__ void __launch_bounds__(256) peer_push_kernel(const PushArgs a) {
   for (int p = 0; p < GemmEpilogue::kMaxPeers; ++p) ep.peer_flag[p] = a.peer_flag[p];
   ep.done_counter = a.done_counter;
   ep.epoch = a.epoch;
+  ep.send_seq = a.send_seq;
   gemm_signal_peers(ep, true);
 }
 
 // A rank whose shard is empty (more ranks than 128-row blocks) computes nothing but still has to tell the others
 // that its part of the epoch is complete.
 __global__ void peer_signal_kernel(GemmEpilogue ep) {
-  if (threadIdx.x < ep.n_peers) *reinterpret_cast<volatile unsigned int *>(ep.peer_flag[threadIdx.x]) = ep.epoch;
+  __shared__ unsigned int epoch;
+  if (threadIdx.x == 0) {
+    epoch = ep.epoch;
+    if (epoch == 0u && ep.send_seq != nullptr) {
+      epoch = *ep.send_seq + 1u;
+      *ep.send_seq = epoch;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < ep.n_peers) *reinterpret_cast<volatile unsigned int *>(ep.peer_flag[threadIdx.x]) = epoch;
 }
 
 }  // namespace
@@ -208,12 +233,14 @@ int q35b_gemm_w4a4_bf16_allgather(const q35b_weight * w, const uint8_t * a_codes
   }
   gather.done_counter = flag_words(buffers[rank]) + kMaxRanks;
   gather.epoch = epoch;
+  gather.send_seq = flag_words(buffers[rank]) + kSendSeqWord;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (w->rows == 0) {
     GemmEpilogue ep;
     ep.n_peers = gather.n_peers;
     for (int i = 0; i < gather.n_peers; ++i) ep.peer_flag[i] = gather.peer_flag[i];
     ep.epoch = epoch;
+    ep.send_seq = gather.send_seq;
     peer_signal_kernel<<<1, 32, 0, s>>>(ep);
     count_launch();
     Q35B_CUDA_TRY(cudaGetLastError(), "peer_signal_kernel launch");
@@ -233,7 +260,7 @@ int q35b_peer_gather_wait(q35b_peer_buffer * const * buffers, int world, int ran
   }
   if (world == 1) return Q35B_OK;
   peer_gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flag_words(buffers[rank]), world, rank, epoch,
-                                                                         status_dev);
+                                                                         status_dev, kGatherWaitLimit);
   count_launch();
   Q35B_CUDA_TRY(cudaGetLastError(), "peer_gather_wait_kernel launch");
   return Q35B_OK;
@@ -273,6 +300,7 @@ int q35b_peer_push(q35b_peer_buffer * const * buffers, int world, int rank, cons
     ++a.n_peers;
   }
   a.done_counter = flag_words(buffers[rank]) + kMaxRanks;
+  a.send_seq = flag_words(buffers[rank]) + kSendSeqWord;
   a.epoch = epoch;
   if (world == 1) return Q35B_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -430,7 +430,7 @@ def gemm_w4a4_gate_up_quant(weight: Nvfp4Weight, a_codes, a_scales_tiled, g, m: 
     _check(lib().q35b_gemm_w4a4_gate_up_nvfp4(weight.handle, a_codes.data_ptr(), a_scales_tiled.data_ptr(), g.data_ptr(), m,
                                               codes.data_ptr(), scales.data_ptr(), out_scale.data_ptr(), st,
                                               _stream_ptr(torch)))
-    return codes.view(m, inter // 2), scales, out_scale
+    return codes.reshape(-1)[:m * (inter // 2)].view(m, inter // 2), scales, out_scale
 
 
 class PeerBuffer:

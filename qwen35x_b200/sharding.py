@@ -76,8 +76,9 @@ class PeerGather:
         gather.project(weight_shard, codes, scales, g)  # GEMM + stores to all ranks + bounded wait
         c = gather.tensor()                             # [m, n] on this rank
 
-    Ranks must call `project` the same number of times (each call is one epoch).  Before reusing the matrix for the
-    next projection every rank must have finished reading it: call `dist.barrier()` or order the work otherwise."""
+    Ranks must call `project` the same number of times: the epochs are counted on the device (epoch argument 0 of
+    the C ABI), so a captured `project` can be replayed as a CUDA graph.  Before reusing the matrix for the next
+    projection every rank must have finished reading it: call `dist.barrier()` or order the work otherwise."""
 
     def __init__(self, m: int, n: int, group=None):
         import torch
@@ -117,15 +118,12 @@ class PeerGather:
             error = e
         agree(error)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.epoch = 0
         dist.barrier(group)
 
     def project(self, weight_shard, a_codes, a_scales_tiled, g):
         from . import engine
 
-        self.epoch += 1
-        engine.gemm_w4a4_allgather(weight_shard, a_codes, a_scales_tiled, g, self.m, self.buffers, self.rank, self.epoch,
-                                   self.status)
+        engine.gemm_w4a4_allgather(weight_shard, a_codes, a_scales_tiled, g, self.m, self.buffers, self.rank, 0, self.status)
         return self.local.tensor()
 
     def tensor(self):
@@ -158,22 +156,27 @@ class MlpLayout:
         self.scale_slots = _round_up(inter // 16, 4)
         self.row_blocks = _round_up(m, 128) // 128
         self.scales_bytes = self.row_blocks * 128 * self.scale_slots
+        self.scales_ld = (self.scale_slots // 4) * 512   # bytes of scale tiles per 128-row block
         self.out_off = _round_up(self.scales_off + self.scales_bytes, 256)
         self.out_ld = hidden * 2
         self.total = _round_up(self.out_off + m * self.out_ld, 256)
 
-    def h_regions(self, col0: int, cols: int):
-        """Regions (offset, rows, row_bytes, ld_bytes) holding columns [col0, col0 + cols) of h: the code bytes of
-        every row, and per 128-row block the run of 512-byte scale tiles of those columns."""
-        assert col0 % 64 == 0 and cols % 64 == 0
-        if cols == 0:
+    def h_regions(self, col0: int, cols: int, row0: int = 0, rows: int | None = None):
+        """Regions (offset, rows, row_bytes, ld_bytes) holding columns [col0, col0 + cols) of rows [row0, row0 + rows)
+        of h: the code bytes of every row, and per 128-row block the run of 512-byte scale tiles of those columns.
+        row0 must be a multiple of 128 (a scale tile is 128 rows high)."""
+        rows = self.m - row0 if rows is None else rows
+        assert col0 % 64 == 0 and cols % 64 == 0 and row0 % 128 == 0
+        if cols == 0 or rows == 0:
             return []
-        return [(self.codes_off + col0 // 2, self.m, cols // 2, self.codes_ld),
-                (self.scales_off + (col0 // 64) * 512, self.row_blocks, (cols // 64) * 512, (self.scale_slots // 4) * 512)]
+        blocks = _round_up(rows, 128) // 128
+        return [(self.codes_off + row0 * self.codes_ld + col0 // 2, rows, cols // 2, self.codes_ld),
+                (self.scales_off + (row0 // 128) * self.scales_ld + (col0 // 64) * 512, blocks, (cols // 64) * 512, self.scales_ld)]
 
-    def out_regions(self, col0: int, cols: int):
+    def out_regions(self, col0: int, cols: int, row0: int = 0, rows: int | None = None):
+        rows = self.m - row0 if rows is None else rows
         assert col0 % 8 == 0 and cols % 8 == 0
-        return [(self.out_off + col0 * 2, self.m, cols * 2, self.out_ld)] if cols else []
+        return [(self.out_off + row0 * self.out_ld + col0 * 2, rows, cols * 2, self.out_ld)] if cols and rows else []
 
 
 class PeerMlp:
@@ -185,45 +188,111 @@ class PeerMlp:
 
     The exchange moves 0.5625 bytes per element of h and 2 bytes per element of the output instead of the BF16
     all-gather of gate/up (4 bytes per element of h).  `buffers` lists every rank's PeerBuffer (buffers[rank] local);
-    in one process all of them can be local (emulated ranks: call `stage(i)` for all ranks in turn)."""
+    in one process all of them can be local (emulated ranks: call `stage(i)` for all ranks in turn).  Epochs are
+    counted on the device, so `run` can be captured in a CUDA graph and replayed; every rank must run the same
+    sequence of blocks with the same `chunks`.
+
+    `run(..., chunks=c)` cuts the tokens into c groups (multiples of 128 rows) and issues the pushes on a second
+    stream, so that the transfer of one group runs under the GEMM of the next."""
 
     def __init__(self, layout: MlpLayout, buffers, rank: int, gate_up_shard, down_shard, h_scale, status):
         self.layout, self.buffers, self.rank = layout, buffers, rank
         self.gate_up, self.down, self.h_scale, self.status = gate_up_shard, down_shard, h_scale, status
         self.world = len(buffers)
-        self.epoch = 0
         raw = buffers[rank].bytes()
         L = layout
         self.h_codes = raw[L.codes_off:L.codes_off + L.m * L.codes_ld]
         self.h_scales = raw[L.scales_off:L.scales_off + L.scales_bytes]
         self.out = buffers[rank].tensor().reshape(-1)[L.out_off // 2:L.out_off // 2 + L.m * L.hidden].view(L.m, L.hidden)
+        self._comm = None
 
-    def stage(self, i: int, a_codes=None, a_scales=None, g=None, residual=None):
-        """Stage 0: gate/up GEMM + push of h; 1: wait for h; 2: down GEMM + push of the output; 3: wait for it."""
+    # -- the four steps on a group of rows [r0, r0 + rows) -------------------------------------------------------
+    def _gate_up(self, a_codes, a_scales, g, r0, rows):
         from . import engine
 
         L = self.layout
-        if i == 0:
-            self.epoch += 2
-            engine.gemm_w4a4_gate_up_quant(self.gate_up, a_codes, a_scales, g, L.m, self.h_scale,
-                                           scratch=(self.h_codes, self.h_scales, None), status=self.status)
-            regs = L.h_regions(self.gate_up.row_begin // 2, self.gate_up.rows // 2)
-            engine.peer_push(self.buffers, self.rank, regs or [(0, 0, 16, 16)], self.epoch - 1)
-        elif i == 1:
-            engine.peer_gather_wait(self.buffers, self.rank, self.epoch - 1, self.status)
-        elif i == 2:
-            col0, cols = self.down.row_begin, self.down.rows
-            if cols:
-                res = residual[:, col0:col0 + cols] if residual is not None else None
-                engine.gemm_w4a4(self.down, self.h_codes.view(L.m, L.codes_ld), self.h_scales, self.h_scale, L.m,
-                                 out=self.out[:, col0:col0 + cols], status=self.status, residual=res)
-            engine.peer_push(self.buffers, self.rank, L.out_regions(col0, cols) or [(0, 0, 16, 16)], self.epoch)
-        else:
-            engine.peer_gather_wait(self.buffers, self.rank, self.epoch, self.status)
+        k = a_codes.shape[1] * 2
+        a_slots = _round_up(k // 16, 4)
+        engine.gemm_w4a4_gate_up_quant(
+            self.gate_up, a_codes[r0:r0 + rows], a_scales[(r0 // 128) * 128 * a_slots:], g, rows, self.h_scale,
+            scratch=(self.h_codes[r0 * L.codes_ld:], self.h_scales[(r0 // 128) * L.scales_ld:], None), status=self.status)
 
-    def run(self, a_codes, a_scales, g, residual=None):
-        self.stage(0, a_codes, a_scales, g)
-        self.stage(1)
-        self.stage(2, residual=residual)
-        self.stage(3)
+    def _push_h(self, r0, rows):
+        from . import engine
+
+        regs = self.layout.h_regions(self.gate_up.row_begin // 2, self.gate_up.rows // 2, r0, rows)
+        engine.peer_push(self.buffers, self.rank, regs or [(0, 0, 16, 16)], 0)
+
+    def _down(self, residual, r0, rows):
+        from . import engine
+
+        L = self.layout
+        col0, cols = self.down.row_begin, self.down.rows
+        if cols:
+            res = residual[r0:r0 + rows, col0:col0 + cols] if residual is not None else None
+            engine.gemm_w4a4(self.down, self.h_codes.view(L.m, L.codes_ld)[r0:r0 + rows], self.h_scales[(r0 // 128) * L.scales_ld:],
+                             self.h_scale, rows, out=self.out[r0:r0 + rows, col0:col0 + cols], status=self.status, residual=res)
+
+    def _push_out(self, r0, rows):
+        from . import engine
+
+        regs = self.layout.out_regions(self.down.row_begin, self.down.rows, r0, rows)
+        engine.peer_push(self.buffers, self.rank, regs or [(0, 0, 16, 16)], 0)
+
+    def _wait(self):
+        from . import engine
+
+        engine.peer_gather_wait(self.buffers, self.rank, 0, self.status)
+
+    def stage(self, i: int, a_codes=None, a_scales=None, g=None, residual=None):
+        """Stage 0: gate/up GEMM + push of h; 1: wait for h; 2: down GEMM + push of the output; 3: wait for it."""
+        m = self.layout.m
+        if i == 0:
+            self._gate_up(a_codes, a_scales, g, 0, m)
+            self._push_h(0, m)
+        elif i == 1:
+            self._wait()
+        elif i == 2:
+            self._down(residual, 0, m)
+            self._push_out(0, m)
+        else:
+            self._wait()
+
+    def run(self, a_codes, a_scales, g, residual=None, chunks: int = 1):
+        import torch
+
+        m = self.layout.m
+        if chunks <= 1 or self.world == 1:
+            for i in range(4):
+                self.stage(i, a_codes, a_scales, g, residual)
+            return self.out
+        # row groups of whole 128-row blocks
+        blocks = _round_up(m, 128) // 128
+        cuts = [min(m, 128 * (blocks * c // chunks)) for c in range(chunks + 1)]
+        groups = [(cuts[c], cuts[c + 1] - cuts[c]) for c in range(chunks) if cuts[c + 1] > cuts[c]]
+        main = torch.cuda.current_stream()
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device=self.out.device)
+        comm = self._comm
+        comm.wait_stream(main)
+        # pushes go to the second stream in the order h(0), h(1), ..., out(0), out(1), ...; the waits on the main
+        # stream come in the same order, which is what the device-counted epochs match
+        for (r0, rows) in groups:
+            self._gate_up(a_codes, a_scales, g, r0, rows)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                self._push_h(r0, rows)
+        for (r0, rows) in groups:
+            self._wait()
+            self._down(residual, r0, rows)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                self._push_out(r0, rows)
+        for _ in groups:
+            self._wait()
+        main.wait_stream(comm)
         return self.out

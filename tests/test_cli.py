@@ -60,3 +60,20 @@ def test_check_and_prefill_modes(engine):
     assert _field(r.stdout, "max_abs_error") < 0.05 and _field(r.stdout, "tflops") > 0
     r = run("--bench-nvfp4-projection", "--nvfp4-projection-kernel", "nonsense", "--synthetic", "64,256")
     assert r.returncode == 10 and "unknown custom NVFP4 projection kernel" in r.stderr
+
+
+@pytest.mark.gpu
+def test_gate_up_and_probe_modes(engine):
+    """--bench-nvfp4-gate-up (src/main.cpp:369, 760-790) and --probe-nvfp4-cublaslt (src/main.cpp:363, 630-680) of
+    the reference's command line: the gate/up pair through one fused decode launch, and one quantised input row
+    through the FP4 tensor-core path against the host value computed from the same quantised input."""
+    r = run("--bench-nvfp4-gate-up", "--synthetic", "3584,1024,5", "--bench-warmup", "2", "--bench-iters", "5")
+    assert r.returncode == 0, r.stderr
+    assert "NVFP4 gate/up benchmark" in r.stdout and "source_shape: 3584x1024" in r.stdout
+    assert _field(r.stdout, "avg_iteration_ms") > 0 and _field(r.stdout, "max_abs_error") < 2e-3
+    r = run("--probe-nvfp4-cublaslt", "--synthetic", "3584,1024,5", "--nvfp4-sample-rows", "16")
+    assert r.returncode == 0, r.stderr
+    assert "NVFP4 cuBLASLt probe" in r.stdout and "sample_rows: 16" in r.stdout
+    expected, actual = _field(r.stdout, "max_abs_expected"), _field(r.stdout, "max_abs_actual")
+    assert expected > 0 and abs(actual - expected) <= 0.02 * expected
+    assert _field(r.stdout, "max_abs_error") <= 0.02 * expected  # same quantised input on both sides: BF16 rounding only

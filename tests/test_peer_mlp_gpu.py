@@ -65,3 +65,50 @@ def test_emulated_ranks_compute_the_same_block(engine, oracle, world, m, hidden,
             assert torch.equal(p.out, exp_out)
         for b in buffers:
             b.bytes()[:layout.total].fill_(0xa5)
+
+
+def test_row_groups_of_the_pipelined_block(engine, oracle):
+    """PeerMlp.run(chunks=c) cuts the tokens into groups of whole 128-row blocks and pushes each group while the next
+    one computes.  Here the same per-group steps are issued rank by rank on one GPU (no launch waits for a later
+    one): offsets of every group into codes, scale tiles and output must land exactly where the unsharded block
+    puts them."""
+    import torch
+
+    from qwen35x_b200 import sharding
+
+    world, m, hidden, inter = 4, 600, 512, 1024
+    gate = make_weight(inter, hidden, seed=21)
+    up = make_weight(inter, hidden, seed=22)
+    down = make_weight(hidden, inter, seed=23)
+    x = to_torch_bf16(make_activations(m, hidden, seed=24))
+    res = to_torch_bf16(make_activations(m, hidden, seed=25))
+    a_codes, a_scales, g = engine.quantize_activations(x)
+    h_scale = torch.tensor([0.004], dtype=torch.float32, device="cuda")
+    _, _, exp_out = _unsharded(engine, torch, m, gate, up, down, a_codes, a_scales, g, h_scale, res)
+    layout = sharding.MlpLayout(m, hidden, inter)
+    buffers = [engine.PeerBuffer.create_bytes(layout.total) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ranks = [sharding.PeerMlp(layout, buffers, r,
+                              engine.Nvfp4Weight.gate_up_from_host(gate[1], gate[2], gate[3], up[1], up[2], up[3],
+                                                                   shard_index=r, shard_count=world),
+                              engine.Nvfp4Weight.from_host(down[1], down[2], down[3], shard_index=r, shard_count=world),
+                              h_scale, status) for r in range(world)]
+    groups = [(0, 256), (256, 256), (512, 88)]
+    for (r0, rows) in groups:
+        for p in ranks:
+            p._gate_up(a_codes, a_scales, g, r0, rows)
+            p._push_h(r0, rows)
+    for p in ranks:
+        for _ in groups:
+            p._wait()
+    for (r0, rows) in groups:
+        for p in ranks:
+            p._down(res, r0, rows)
+            p._push_out(r0, rows)
+    for p in ranks:
+        for _ in groups:
+            p._wait()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for p in ranks:
+        assert torch.equal(p.out, exp_out)
