@@ -52,6 +52,9 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 amax_to_global_scale_kernel(const T * __restrict__ x, size_t n, unsigned int * __restrict__ ws,
                             float * __restrict__ g_out) {
+  // no early griddepcontrol.launch_dependents here: a dependent grid that became resident early would take the
+  // registers this kernel's remaining blocks need; the implicit trigger at block exit overlaps the tail only
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the kernel before
   float local = 0.0f;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   if constexpr (sizeof(T) == 2) {
@@ -134,6 +137,7 @@ __global__ void __launch_bounds__(kThreads)
 quantize_nvfp4_kernel(const T * __restrict__ x, int rows, int rows_padded, int k, const float * __restrict__ g_dev,
                       float g_fixed, float * __restrict__ g_out, int swap, uint8_t * __restrict__ codes,
                       uint8_t * __restrict__ scales) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the per-tensor scale, and x itself, may come from the kernel before
   const int scale_cols = k >> 4;
   const int slots = ((scale_cols + 3) >> 2) << 2;  // block slots per row, a multiple of 4
   const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -215,9 +219,9 @@ int launch_amax(const T * x, size_t n, unsigned int * ws, float * g_out, cudaStr
   const size_t per_block = static_cast<size_t>(kThreads) * 8 * 4;
   int blocks = static_cast<int>(std::min<size_t>((n + per_block - 1) / per_block, static_cast<size_t>(sm_count()) * 4));
   if (blocks < 1) blocks = 1;
-  amax_to_global_scale_kernel<T><<<blocks, kThreads, 0, s>>>(x, n, ws, g_out);
+  const cudaError_t le = launch_pdl(amax_to_global_scale_kernel<T>, dim3(blocks), dim3(kThreads), 0, s, x, n, ws, g_out);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "amax_to_global_scale_kernel launch");
+  Q35B_CUDA_TRY(le, "amax_to_global_scale_kernel launch");
   return Q35B_OK;
 }
 
@@ -238,10 +242,10 @@ int launch_quantize_activations(const T * x, int m, int k, float global_scale, u
   const int rows_padded = round_up_int(m, 128);
   const size_t threads = static_cast<size_t>(rows_padded) * ((((k >> 4) + 3) >> 2) << 2);
   const unsigned blocks = static_cast<unsigned>((threads + kThreads - 1) / kThreads);
-  quantize_nvfp4_kernel<T, kEngine, true><<<blocks, kThreads, 0, s>>>(
-    x, m, rows_padded, k, dynamic ? g_dev : nullptr, global_scale, dynamic ? nullptr : g_dev, 0, codes, scales_tiled);
+  const cudaError_t le = launch_pdl(quantize_nvfp4_kernel<T, kEngine, true>, dim3(blocks), dim3(kThreads), 0, s, x, m, rows_padded, k,
+                                    dynamic ? g_dev : nullptr, global_scale, dynamic ? nullptr : g_dev, 0, codes, scales_tiled);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "quantize_nvfp4_kernel launch");
+  Q35B_CUDA_TRY(le, "quantize_nvfp4_kernel launch");
   return Q35B_OK;
 }
 

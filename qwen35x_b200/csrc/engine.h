@@ -29,6 +29,25 @@ inline void count_launch(unsigned n = 1) { g_launches.fetch_add(n, std::memory_o
 
 int sm_count();
 
+// Launch with programmatic stream serialisation: the grid may be scheduled while the previous kernel of the stream is
+// still finishing.  Every kernel launched this way executes griddepcontrol.wait before its first access to global
+// memory, which returns only when everything earlier in the stream is complete and visible, so what overlaps is
+// launch latency and the prologue (barrier set-up, TMEM allocation), never data.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Q35B_OK when the weight lives on the calling thread's current device, else Q35B_ERR_ARGUMENT: every launch goes
 // to the current device, and a weight of another GPU would be read through a pointer that device cannot reach.
 int check_weight_device(const struct ::q35b_weight * w);

@@ -32,7 +32,7 @@ namespace q35b {
 namespace {
 
 #ifndef Q35B_TILE_N
-#define Q35B_TILE_N 192
+#define Q35B_TILE_N 256
 #endif
 constexpr int kCtaRows = 128;            // rows of A staged per CTA
 constexpr int kTileM = 256;              // output tile of the pair: 256 tokens ...
@@ -230,6 +230,10 @@ gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t tmem_acc = tmem_base;
   const uint32_t tmem_sfa = tmem_base + kAccCols;
   const uint32_t tmem_sfb = tmem_sfa + kSfaCols;
+  // Launched with programmatic stream serialisation: everything above (barriers, TMEM, the pair's rendezvous) may run
+  // under the tail of the previous kernel; nothing below touches global memory before that kernel is complete.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // An error recorded by an earlier launch: run no tiles (every CTA still goes through alloc, barriers, dealloc).
   const bool aborted = *reinterpret_cast<volatile unsigned int *>(status) != 0u;
 
@@ -452,11 +456,11 @@ int launch_gemm_w4a4_2cta(const q35b_weight * w, const uint8_t * a_codes, const 
   const int n_tiles = (w->rows + kTileN - 1) / kTileN;
   const int num_tiles = m_tiles * n_tiles;
   const int pairs = std::max(1, std::min(num_tiles, sm_count() / 2));
-  gemm_w4a4_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, s>>>(tmap_a, w->tmap2_codes, tmap_sfa, w->tmap2_sf, g_dev, ep, m,
-                                                               w->rows, w->k / 2, m_tiles, num_tiles,
-                                                               static_cast<__nv_bfloat16 *>(c_bf16), ldc, status_dev);
+  const cudaError_t le = launch_pdl(gemm_w4a4_2cta_kernel, dim3(2 * pairs), dim3(kThreads), kSmemBytes, s, tmap_a, w->tmap2_codes,
+                                    tmap_sfa, w->tmap2_sf, g_dev, ep, m, w->rows, w->k / 2, m_tiles, num_tiles,
+                                    static_cast<__nv_bfloat16 *>(c_bf16), ldc, status_dev);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "gemm_w4a4_2cta_kernel launch");
+  Q35B_CUDA_TRY(le, "gemm_w4a4_2cta_kernel launch");
   return Q35B_OK;
 }
 

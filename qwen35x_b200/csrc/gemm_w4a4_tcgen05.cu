@@ -206,6 +206,10 @@ gemm_w4a4_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int sf_col_blocks = k_bytes >> 5;                        // K/64: 512-byte scale tiles per row block
   const int k_steps = (sf_col_blocks + kMmaPerStage - 1) / kMmaPerStage;
 
+  // Launched with programmatic stream serialisation: the grid may be scheduled under the tail of the previous kernel,
+  // but reads and writes nothing before that kernel is complete.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // A tile that finds an error already recorded does nothing: after one expired wait the rest of the grid drains.
   __shared__ unsigned int s_abort;
   if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile unsigned int *>(status);
@@ -390,11 +394,11 @@ int launch_tile(const q35b_weight * w, const CUtensorMap & tmap_a, const uint8_t
     attr_set[w->device & 63].store(true, std::memory_order_release);
   }
   const dim3 grid((w->rows + BLOCK_N - 1) / BLOCK_N, (m + kBlockM - 1) / kBlockM);
-  kernel<<<grid, kThreads, C::kSmemBytes, s>>>(tmap_a, BLOCK_N == 256 ? w->tmap_codes_256 : w->tmap_codes_128, a_scales,
-                                               w->scales_tiled, g_dev, ep, m, w->rows, w->k / 2, (w->rows + 127) / 128,
-                                               static_cast<__nv_bfloat16 *>(c), ldc, status);
+  const cudaError_t le = launch_pdl(kernel, grid, dim3(kThreads), C::kSmemBytes, s, tmap_a,
+                                    BLOCK_N == 256 ? w->tmap_codes_256 : w->tmap_codes_128, a_scales, w->scales_tiled, g_dev, ep, m,
+                                    w->rows, w->k / 2, (w->rows + 127) / 128, static_cast<__nv_bfloat16 *>(c), ldc, status);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "gemm_w4a4_tcgen05_kernel launch");
+  Q35B_CUDA_TRY(le, "gemm_w4a4_tcgen05_kernel launch");
   return Q35B_OK;
 }
 
