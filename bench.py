@@ -290,7 +290,7 @@ def run_engine(args, rank: int, world: int, local_rank: int) -> dict | None:
     stream = torch.cuda.Stream(device=device)
 
     # The step's work list: all 96 projections in one persistent launch (they are independent in this workload).
-    batches = [q.GemvBatch(list(zip(models[s], xs, ys)), args.m) for s in range(sets)]
+    batches = [q.GemvBatch(list(zip(models[s], xs, ys)), args.m, digits=args.digits) for s in range(sets)]
 
     def step_per_projection(set_index: int):
         for w, x, y in zip(models[set_index], xs, ys):
@@ -977,6 +977,9 @@ def main() -> int:
     ap.add_argument("--impl", choices=["engine", "reference"], default="engine")
     ap.add_argument("--m", type=int, default=1, choices=range(1, 9), metavar="TOKENS",
                     help="tokens per decode step (1..8); the headline and the driver's runs use 1")
+    ap.add_argument("--digits", type=int, default=0,
+                    help="decode step on the tensor cores with this many NVFP4 digit rows per token (0: the exact "
+                         "BF16-activation kernel)")
     ap.add_argument("--report", default="", help="write the per-shape throughput report (JSON) to this path and exit")
     ap.add_argument("--only", choices=["all", "decode", "gemm"], default="all",
                     help="profiling aid: 'decode' skips the GEMM, the per-projection-launch figure and the CPU "

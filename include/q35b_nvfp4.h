@@ -177,6 +177,21 @@ Q35B_API size_t q35b_gemv_item_bytes(void);
 typedef struct q35b_gemv_batch q35b_gemv_batch;
 /* Builds the tile schedule and uploads the descriptors (allocates, synchronises). */
 Q35B_API int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out);
+/* The same work list on the tensor cores (no counterpart in the reference, whose decode dequantises in registers,
+ * src/kernels/cuda/decode_layers.cuh:200-261): the weight streams through tcgen05.mma as the 128-row operand and
+ * every token's BF16 activations enter as `digits` rows of NVFP4, a digit expansion computed on the device before
+ * each run: digit j quantises (16-element blocks, E4M3 block scale, one fp32 scale per token) what digits 0..j-1
+ * left over, so their sum reproduces the activation to within 6^-digits of its block's largest element (5 digits:
+ * 1.3e-4 at worst; BF16's own rounding step is 3.9e-3).  Outputs stay within the relative L2 bound of 1e-3 against
+ * the exact W4A16 result.  Measured on B200 it is NOT the faster path: 73 us per 0.8B-class step at one token and
+ * 96 us at eight, against 49 and 88 us for q35b_gemv_batch_create (with operand tiles this narrow the tensor pipe's
+ * copy-to-MMA turnaround per 256 columns of K sets the pace); it is kept as the variant whose cost does not grow
+ * with the conversion work and as the decode-side user of the weight-streaming kernel.  Items must be independent
+ * (after = 0); non-finite activations count as zero.  digits: 1..8 with m * digits <= 128; 5 is the intended
+ * setting.  q35b_gemv_batch_run launches two kernels (the expansion, then the projection, whose weight stream
+ * starts at once). */
+Q35B_API int q35b_gemv_batch_create_tensor(const q35b_gemv_item * items, int count, int m, int digits,
+                                           q35b_gemv_batch ** out);
 /* One kernel launch on `stream`; no allocation, no synchronisation.  The launch uses programmatic stream
  * serialisation: the kernel may begin streaming WEIGHTS while the previous kernel of the stream is still finishing
  * (activations, residuals and outputs are touched only after that kernel is complete).  Weights are therefore
@@ -187,6 +202,15 @@ Q35B_API void q35b_gemv_batch_destroy(q35b_gemv_batch * batch);
 /* Copies the batch's device status word to the host (synchronises): 0, or the code of a bounded device-side wait
  * that expired during a run. */
 Q35B_API int q35b_gemv_batch_status(const q35b_gemv_batch * batch, unsigned int * status_out);
+/* Test hook for the bounded device-side waits of a work list built by q35b_gemv_batch_create: every wait of the
+ * following runs (ring barriers, activation hand-over, dependency poll) gives up after `wait_limit_polls` polls
+ * instead of 2^22, and a dependent item demands `extra_completions` more completions of the item it runs after than
+ * that item can deliver.  With a small limit and one extra completion the dependency poll runs out within
+ * microseconds, 15 lands in the status word, the remaining roles run out on their own waits and the kernel returns:
+ * what an item whose producer never finishes looks like, without a kernel that hangs.  (0 extra completions and
+ * 1 << 22 polls restore normal operation.)  Also clears the list's status word and completion counts. */
+Q35B_API int q35b_debug_gemv_batch_wait(q35b_gemv_batch * batch, unsigned int wait_limit_polls,
+                                        unsigned int extra_completions);
 /* Weight bytes (codes + scales) one run streams. */
 Q35B_API size_t q35b_gemv_batch_stream_bytes(const q35b_gemv_batch * batch);
 

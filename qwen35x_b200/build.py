@@ -18,7 +18,7 @@ LIB_DIR = PKG / "_lib"
 LIB = LIB_DIR / "libq35b.so"
 CLI = LIB_DIR / "q35b"
 
-SOURCES = ["api.cu", "gemv_w4a16.cu", "gemv_stream.cu", "act_quant.cu", "gemm_w4a4_tcgen05.cu", "gemm_w4a4_2cta.cu", "static_prefill.cu", "peer_gather.cu"]
+SOURCES = ["api.cu", "gemv_w4a16.cu", "gemv_stream.cu", "act_quant.cu", "gemm_w4a4_tcgen05.cu", "gemm_w4a4_2cta.cu", "gemm_wstream.cu", "static_prefill.cu", "peer_gather.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2", "--expt-relaxed-constexpr",

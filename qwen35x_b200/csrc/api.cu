@@ -336,6 +336,10 @@ int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int m, q35b_
   return gemv_batch_build(items, count, m, out);
 }
 
+int q35b_gemv_batch_create_tensor(const q35b_gemv_item * items, int count, int m, int digits, q35b_gemv_batch ** out) {
+  return gemv_batch_build_tensor(items, count, m, digits, out);
+}
+
 int q35b_gemv_batch_run(const q35b_gemv_batch * batch, q35b_stream stream) {
   return gemv_batch_launch(batch, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
@@ -344,6 +348,10 @@ void q35b_gemv_batch_destroy(q35b_gemv_batch * batch) { gemv_batch_free(batch); 
 
 int q35b_gemv_batch_status(const q35b_gemv_batch * batch, unsigned int * status_out) {
   return gemv_batch_read_status(batch, status_out);
+}
+
+int q35b_debug_gemv_batch_wait(q35b_gemv_batch * batch, unsigned int wait_limit_polls, unsigned int extra_completions) {
+  return gemv_batch_debug_wait(batch, wait_limit_polls, extra_completions);
 }
 
 size_t q35b_gemv_batch_stream_bytes(const q35b_gemv_batch * batch) { return gemv_batch_bytes(batch); }

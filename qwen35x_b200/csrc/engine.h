@@ -107,10 +107,12 @@ int launch_tile_scales(const uint8_t * scales_rowmajor, int rows, int scale_cols
 // gemv_stream.cu
 bool gemv_stream_eligible(const q35b_weight * w, int m);
 int gemv_batch_build(const q35b_gemv_item * items, int count, int m, struct q35b_gemv_batch ** out);
+int gemv_batch_build_tensor(const q35b_gemv_item * items, int count, int m, int digits, struct q35b_gemv_batch ** out);
 int gemv_batch_launch(const struct q35b_gemv_batch * b, const void * x_override, void * y_override, cudaStream_t s);
 void gemv_batch_free(struct q35b_gemv_batch * b);
 int gemv_batch_read_status(const struct q35b_gemv_batch * b, unsigned int * out);
 size_t gemv_batch_bytes(const struct q35b_gemv_batch * b);
+int gemv_batch_debug_wait(struct q35b_gemv_batch * b, unsigned int wait_limit, unsigned int extra_completions);
 
 // gemm_w4a4_tcgen05.cu
 int make_code_map(CUtensorMap * map, const void * base, int rows, int k_bytes, int box_rows);
@@ -142,6 +144,19 @@ int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8
                      int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
                      cudaStream_t s, const GemmQuantOut * qout = nullptr, const GemmGather * gather = nullptr);
 
+
+// gemm_wstream.cu: weight-streaming projection for 1..128 operand rows (small-M prefill, tensor-core decode)
+bool gemm_wstream_eligible(const q35b_weight * w, int m);
+int launch_gemm_wstream(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled, const float * g_dev,
+                        int m, void * c_bf16, int ldc, const void * residual_bf16, int ldr, unsigned int * status_dev,
+                        cudaStream_t s);
+
+struct WBatch;  // decode work list on the tensor path (digit-expanded activations)
+int wbatch_build(const q35b_gemv_item * items, int count, int m, int digits, WBatch ** out);
+int wbatch_launch(const WBatch * b, cudaStream_t s);
+void wbatch_free(WBatch * b);
+int wbatch_status(const WBatch * b, unsigned int * out);
+size_t wbatch_bytes(const WBatch * b);
 
 // gemm_w4a4_2cta.cu
 bool gemm_2cta_eligible(const q35b_weight * w, int m);

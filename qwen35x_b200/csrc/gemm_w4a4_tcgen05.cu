@@ -509,6 +509,11 @@ int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8
   if (gemm_2cta_eligible(w, m)) {
     return launch_gemm_w4a4_2cta(w, a_codes, a_scales_tiled, g_dev, m, c_bf16, ldc, ep, status_dev, s);
   }
+  // Up to 128 tokens: the weight streams through the 128-row side of the tile, every SM takes row blocks
+  // (gemm_wstream.cu); bound by HBM, not by the tensor pipe.
+  if (qout == nullptr && gather == nullptr && gemm_wstream_eligible(w, m)) {
+    return launch_gemm_wstream(w, a_codes, a_scales_tiled, g_dev, m, c_bf16, ldc, residual_bf16, ldr, status_dev, s);
+  }
   CUtensorMap tmap_a;
   if (const int st = make_code_map(&tmap_a, a_codes, m, w->k / 2, kBlockM)) return st;
   // Small problems get narrower tiles so that more SMs have work.

@@ -102,8 +102,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t ok;
     asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -175,7 +175,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
                          const int * __restrict__ cta_begin, int m_tokens, const __nv_bfloat16 * x_override,
                          __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
                          int x_raw_bytes, int x_raw_depth, int x_bufs, unsigned long long * item_done,
-                         int counted_items, unsigned int * status) {
+                         int counted_items, unsigned int * status, uint32_t wait_limit, unsigned int wait_extra) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled code tiles; pointer arithmetic on the __shared__ array (rather than an
   // integer round trip) keeps every later access a shared-memory access for the compiler.
@@ -246,7 +246,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const uint8_t * sc = tile->scales;
         const int row0 = tile->row_block * kTileRows;
         for (int ks = 0; ks < k_steps; ++ks) {
-          if (!mbar_wait(smem_u32(empty + stage), phase ^ 1)) {
+          if (!mbar_wait(smem_u32(empty + stage), phase ^ 1, wait_limit)) {
             atomicExch(status, kProducerWait);
             ok = false;
             break;
@@ -278,8 +278,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       int met = 0;
       if (lane == 0) {
         const volatile unsigned long long * cnt = item_done + tl->wait_item;
-        for (uint32_t i = 0; i < kWaitLimit; ++i) {
-          if (*cnt >= tl->wait_count) {
+        for (uint32_t i = 0; i < wait_limit; ++i) {
+          if (*cnt >= tl->wait_count + wait_extra) {
             met = 1;
             break;
           }
@@ -331,8 +331,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       const int buf = (x_bufs == 2) ? (xi & 1) : 0;
       const uint32_t xphase = (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1);
       const uint32_t rb = x_raw_depth > 0 ? xi % x_raw_depth : 0;
-      if ((x_raw_depth > 0 && !mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1)) ||
-          !mbar_wait(smem_u32(xempty + buf), xphase ^ 1)) {
+      if ((x_raw_depth > 0 && !mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1, wait_limit)) ||
+          !mbar_wait(smem_u32(xempty + buf), xphase ^ 1, wait_limit)) {
         if (lane == 0) atomicExch(status, kPrepWait);
         break;
       }
@@ -424,7 +424,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         }
         prev_item = tile->item;
         buf = (x_bufs == 2) ? (xi & 1) : 0;
-        if (!mbar_wait(smem_u32(xfull + buf), (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1))) {
+        if (!mbar_wait(smem_u32(xfull + buf), (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1), wait_limit)) {
           if (lane == 0) atomicExch(status, kConsumerXWait);
           ok = false;
           break;
@@ -455,7 +455,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         bstep[ts] = owner ? 256 : 0;
       }
       for (int ks = 0; ks < k_steps; ++ks) {
-        if (!mbar_wait(smem_u32(full + stage), phase)) {
+        if (!mbar_wait(smem_u32(full + stage), phase, wait_limit)) {
           if (lane == 0) atomicExch(status, kConsumerWait);
           ok = false;
           break;
@@ -511,7 +511,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       const uint32_t rphase = (ti >> 1) & 1;
       float * slot = red + ((rb * kRowGroups + rg) * 32 + lane) * 4 * MT;
       if (kh == 1) {
-        if (!mbar_wait(smem_u32(red_free + rb), rphase ^ 1)) {
+        if (!mbar_wait(smem_u32(red_free + rb), rphase ^ 1, wait_limit)) {
           if (lane == 0) atomicExch(status, kConsumerWait);
           ok = false;
           break;
@@ -522,7 +522,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(red_full + rb));
       } else {
-        if (!mbar_wait(smem_u32(red_full + rb), rphase)) {
+        if (!mbar_wait(smem_u32(red_full + rb), rphase, wait_limit)) {
           if (lane == 0) atomicExch(status, kConsumerWait);
           ok = false;
           break;
@@ -668,6 +668,9 @@ struct q35b_gemv_batch {
   unsigned long long * item_done = nullptr;  // per item: storing warps that finished a tile in the current run
   bool has_dependencies = false;
   size_t bytes_per_run = 0;
+  uint32_t wait_limit = kWaitLimit;   // polls every device-side wait of a run may take
+  unsigned int wait_extra = 0;        // test hook: completions demanded on top of what a dependency really delivers
+  q35b::WBatch * tensor = nullptr;   // set: the list runs on the tensor path (gemm_wstream.cu), nothing above is used
 };
 
 namespace q35b {
@@ -836,8 +839,23 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
   return Q35B_OK;
 }
 
+int gemv_batch_build_tensor(const q35b_gemv_item * items, int count, int m, int digits, q35b_gemv_batch ** out) {
+  if (out == nullptr) return fail(Q35B_ERR_ARGUMENT, "Invalid NVFP4 projection work list.");
+  *out = nullptr;
+  WBatch * t = nullptr;
+  if (const int st = wbatch_build(items, count, m, digits, &t)) return st;
+  auto * b = new q35b_gemv_batch();
+  b->count = count;
+  b->m = m;
+  b->tensor = t;
+  b->bytes_per_run = wbatch_bytes(t);
+  *out = b;
+  return Q35B_OK;
+}
+
 int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void * y_override, cudaStream_t s) {
   if (b == nullptr) return fail(Q35B_ERR_ARGUMENT, "Null NVFP4 projection work list.");
+  if (b->tensor != nullptr) return wbatch_launch(b->tensor, s);
   const auto * xo = static_cast<const __nv_bfloat16 *>(x_override);
   auto * yo = static_cast<__nv_bfloat16 *>(y_override);
   const int counted = b->has_dependencies ? b->count : 0;
@@ -857,7 +875,8 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   const Plan & pl = b->plan;
   const cudaError_t le = cudaLaunchKernelEx(&cfg, b->m <= 4 ? gemv_w4a16_stream_kernel<1> : gemv_w4a16_stream_kernel<2>, d_items,
                                             d_tiles, d_begin, b->m, xo, yo, pl.stages, pl.x_buf_halfs, pl.xs_buf_floats,
-                                            pl.x_raw_bytes, pl.x_raw_depth, pl.x_bufs, b->item_done, counted, b->status);
+                                            pl.x_raw_bytes, pl.x_raw_depth, pl.x_bufs, b->item_done, counted, b->status, b->wait_limit,
+                                            b->wait_extra);
   count_launch();
   Q35B_CUDA_TRY(le, "gemv_w4a16_stream_kernel launch");
   return Q35B_OK;
@@ -865,16 +884,29 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
 
 void gemv_batch_free(q35b_gemv_batch * b) {
   if (b == nullptr) return;
+  wbatch_free(b->tensor);
   if (b->dev_base != nullptr) cudaFree(b->dev_base);
   delete b;
 }
 
 int gemv_batch_read_status(const q35b_gemv_batch * b, unsigned int * out) {
   if (b == nullptr || out == nullptr) return fail(Q35B_ERR_ARGUMENT, "Null NVFP4 projection work list.");
+  if (b->tensor != nullptr) return wbatch_status(b->tensor, out);
   Q35B_CUDA_TRY(cudaMemcpy(out, b->status, sizeof(unsigned int), cudaMemcpyDeviceToHost), "cudaMemcpy(work list status)");
   return Q35B_OK;
 }
 
 size_t gemv_batch_bytes(const q35b_gemv_batch * b) { return b ? b->bytes_per_run : 0; }
+
+int gemv_batch_debug_wait(q35b_gemv_batch * b, unsigned int wait_limit, unsigned int extra_completions) {
+  if (b == nullptr || b->tensor != nullptr || wait_limit == 0) return fail(Q35B_ERR_ARGUMENT, "Invalid NVFP4 projection work list.");
+  b->wait_limit = wait_limit;
+  b->wait_extra = extra_completions;
+  // counts of a run that gave up stay behind: start the next run from zero
+  if (b->item_done != nullptr) {
+    Q35B_CUDA_TRY(cudaMemset(b->status, 0, 16 + sizeof(unsigned long long) * (b->count + 1)), "cudaMemset(work list counters)");
+  }
+  return Q35B_OK;
+}
 
 }  // namespace q35b

@@ -66,12 +66,16 @@ def lib() -> C.CDLL:
     L.q35b_gemv_w4a16_f32.argtypes = [vp, vp, f, vp, i, vp]
     L.q35b_gemv_batch_create.restype = i
     L.q35b_gemv_batch_create.argtypes = [vp, i, i, C.POINTER(vp)]
+    L.q35b_gemv_batch_create_tensor.restype = i
+    L.q35b_gemv_batch_create_tensor.argtypes = [vp, i, i, i, C.POINTER(vp)]
     L.q35b_gemv_batch_run.restype = i
     L.q35b_gemv_batch_run.argtypes = [vp, vp]
     L.q35b_gemv_batch_destroy.restype = None
     L.q35b_gemv_batch_destroy.argtypes = [vp]
     L.q35b_gemv_batch_status.restype = i
     L.q35b_gemv_batch_status.argtypes = [vp, C.POINTER(C.c_uint)]
+    L.q35b_debug_gemv_batch_wait.restype = i
+    L.q35b_debug_gemv_batch_wait.argtypes = [vp, C.c_uint, C.c_uint]
     L.q35b_gemv_batch_stream_bytes.restype = sz
     L.q35b_gemv_batch_stream_bytes.argtypes = [vp]
     L.q35b_act_codes_bytes.restype = sz
@@ -282,7 +286,9 @@ class GemvBatch:
     with out_rows = rows/2; `after` = index of an earlier item whose y this item's x is (the down projection after
     gate/up) -- items without it are independent.  The tensors must stay alive and in place for the life of the batch."""
 
-    def __init__(self, items, m: int):
+    def __init__(self, items, m: int, digits: int = 0):
+        """digits > 0: run the list on the tensor cores with every token's activations expanded into that many NVFP4
+        digit rows (q35b_gemv_batch_create_tensor; 5 is the intended setting); 0: BF16 activations carried exactly."""
         torch = _torch()
         self._keep = list(items)
         arr = (_GemvItem * len(self._keep))()
@@ -299,8 +305,12 @@ class GemvBatch:
             arr[j] = _GemvItem(w.handle.value, x.data_ptr(), y.data_ptr(), res.data_ptr() if res is not None else None,
                                after + 1)
         h = C.c_void_p()
-        _check(lib().q35b_gemv_batch_create(arr, len(self._keep), m, C.byref(h)))
+        if digits > 0:
+            _check(lib().q35b_gemv_batch_create_tensor(arr, len(self._keep), m, digits, C.byref(h)))
+        else:
+            _check(lib().q35b_gemv_batch_create(arr, len(self._keep), m, C.byref(h)))
         self._h = h
+        self.digits = digits
         self.m = m
         self.stream_bytes = int(lib().q35b_gemv_batch_stream_bytes(h))
 
@@ -311,6 +321,10 @@ class GemvBatch:
         out = C.c_uint(0)
         _check(lib().q35b_gemv_batch_status(self._h, C.byref(out)))
         return int(out.value)
+
+    def debug_wait(self, wait_limit_polls: int, extra_completions: int) -> None:
+        """Test hook (q35b_debug_gemv_batch_wait): short wait limit and extra completions demanded of dependencies."""
+        _check(lib().q35b_debug_gemv_batch_wait(self._h, wait_limit_polls, extra_completions))
 
     def close(self) -> None:
         if self._h is not None and self._h.value:

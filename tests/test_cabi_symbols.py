@@ -84,6 +84,6 @@ def test_shape_report_renders_markdown():
     }
     md = shape_report.to_markdown(report)
     for needle in ("| step | 1 | 96 | 234.6 | 50.00 | 4691.6 | 0.717 | `gemv_w4a16_stream_kernel` |", "| one | 1 | 3584 | 1024 |",
-                   "| gemm | 512 | 18432 | 2560 | 48.3 | 10.00 | 100.0 | 0.011 | 0.015 | 10.00 | `gemm_w4a4_2cta_kernel` |",
+                   "| gemm | 512 | 18432 | 2560 | 48.3 | 10.00 | 100.0 | 0.011 | 0.015 | - | 10.00 | - | `gemm_w4a4_2cta_kernel` |",
                    "| mlp | 4096 | 2560 | 9216 | 579.8 | 248.30 | 2335.1 | 205.40 | 2823.4 |", "| (3584, 1024, 1) | 39418 | 4600 | 16 | 1024 rows |"):
         assert needle in md, needle

@@ -311,3 +311,41 @@ def test_work_list_dependency_must_point_backwards(engine):
 
     h = ctypes.c_void_p()
     assert engine.lib().q35b_gemv_batch_create(arr, 1, 1, ctypes.byref(h)) == 1  # item 0 cannot run after item 0
+
+
+def test_dependency_wait_that_cannot_be_met_expires(engine, oracle):
+    """A dependent item whose producer never delivers the completions it waits for: with the test hook's short limit
+    on every device-side wait the dependency poll runs out, 15 lands in the status word, the other roles run out on
+    their own waits and the kernel returns within milliseconds; the context stays usable and, with the hook switched
+    off again, the same list computes the right result."""
+    import time
+
+    import torch
+
+    m, hidden, inter = 2, 512, 1024
+    _, g_codes, g_scales, g_s2 = make_weight(inter, hidden, seed=1)
+    _, u_codes, u_scales, u_s2 = make_weight(inter, hidden, seed=2)
+    _, d_codes, d_scales, d_s2 = make_weight(hidden, inter, seed=3)
+    gu = engine.Nvfp4Weight.gate_up_from_host(g_codes, g_scales, g_s2, u_codes, u_scales, u_s2)
+    down = engine.Nvfp4Weight.from_host(d_codes, d_scales, d_s2)
+    xb = make_activations(m, hidden, seed=4)
+    x = to_torch_bf16(xb)
+    h = torch.zeros((m, inter), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((m, hidden), dtype=torch.bfloat16, device="cuda")
+    batch = engine.GemvBatch([(gu, x, h), (down, h, y, None, 0)], m)
+    batch.run()
+    torch.cuda.synchronize()
+    assert batch.status() == 0
+    good = y.clone()
+    batch.debug_wait(4096, 1)  # one completion more than item 0 can ever report
+    t0 = time.perf_counter()
+    batch.run()
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 2.0
+    assert batch.status() == 15
+    assert float(torch.ones(8, device="cuda").sum().item()) == 8.0  # the context is alive
+    batch.debug_wait(1 << 22, 0)
+    y.zero_()
+    batch.run()
+    torch.cuda.synchronize()
+    assert batch.status() == 0 and torch.equal(y, good)

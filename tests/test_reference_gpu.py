@@ -70,3 +70,44 @@ def test_reference_activation_quantiser_bytes(engine, oracle, ref):
     assert np.array_equal(scales.cpu().numpy(), oracle.swizzle_scales(e_scales))
     c2, s2 = engine.quantize_activations_reference_recipe(x, swap_nibbles=True)
     assert torch.equal(c2, codes) and torch.equal(s2, scales)
+
+
+def test_w4a4_gemm_matches_the_reference_cublaslt_bridge(engine, oracle, ref):
+    """Pins the W4A4 projection to an output of the reference itself: run_nvfp4_cublaslt_prefill_projection_device_bf16
+    (src/runtime/cuda_bench.cu:1056-1167 behind include/qwen35x/runtime/cuda_bench.h:70-83: the reference's
+    quantiser + cuBLASLt FP4 matmul, fp32 output) against the engine's tcgen05 GEMM fed with activations quantised
+    by the reference's own recipe (no per-tensor scale: g = 1).  Same codes, same scale bytes, same formula: the
+    outputs may differ by accumulation order and by the BF16 rounding of the engine's output only."""
+    import ctypes as C
+
+    import torch
+
+    for (m, n, k) in ((300, 1024, 1024), (64, 512, 2560), (16, 3584, 1024)):
+        _, codes, scales, s2 = make_weight(n, k, seed=n + k)
+        xb = make_activations(m, k, seed=m, outlier_frac=0.001)
+        x = to_torch_bf16(xb)
+        swapped = ((codes & 0x0F) << 4) | (codes >> 4)
+        d_w = torch.from_numpy(swapped).cuda()
+        d_ws = torch.from_numpy(oracle.swizzle_scales(scales)).cuda()
+        d_s2 = torch.tensor([s2], dtype=torch.float32, device="cuda")
+        d_ac = torch.zeros(m * k // 2, dtype=torch.uint8, device="cuda")
+        d_as = torch.zeros(oracle.tiled_scale_bytes(m, k // 16), dtype=torch.uint8, device="cuda")
+        d_c = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        rc = ref.ref_cublaslt_prefill_bf16(x.data_ptr(), d_w.data_ptr(), d_ws.data_ptr(), d_s2.data_ptr(), m, n, k,
+                                           d_ac.data_ptr(), d_as.data_ptr(), d_c.data_ptr(), None)
+        if rc != 0:
+            pytest.skip(f"the reference's cuBLASLt FP4 bridge does not run here: {ref.ref_last_error().decode()}")
+        torch.cuda.synchronize()
+        expected = d_c.cpu().numpy()
+        w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+        a_codes, a_scales = engine.quantize_activations_reference_recipe(x, swap_nibbles=False)
+        one = torch.ones(1, dtype=torch.float32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        c = engine.gemm_w4a4(w, a_codes, a_scales, one, m, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        got = oracle.bf16_to_f32(from_torch_bf16(c))
+        exp_bf16 = oracle.bf16_to_f32(oracle.bf16_round(expected))
+        assert oracle.rel_l2(got, exp_bf16) <= 1e-3, (m, n, k, oracle.rel_l2(got, exp_bf16))
+        assert oracle.rel_l2(got, expected) <= 3e-3  # against the unrounded fp32 output: BF16 rounding of ours on top

@@ -24,11 +24,17 @@ def _both_paths(engine, w, x):
     m = x.shape[0]
     expected = engine.project_prefill(w, x)
     got = torch.full((m, w.rows), float("nan"), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = L.q35b_project_prefill_bf16_static(w.handle, C.c_void_p(x.data_ptr()), m, C.c_float(0.0),
                                             C.c_void_p(got.data_ptr()), got.stride(0),
                                             C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, L.q35b_last_error()
     torch.cuda.synchronize()
+    # the call took no device memory (the driver's free-memory figure is what any allocation would move) ...
+    assert torch.cuda.mem_get_info()[0] == free_before
+    # ... and none of its bounded device-side waits expired
+    assert engine.static_prefill_status() == 0
     return got, expected
 
 
