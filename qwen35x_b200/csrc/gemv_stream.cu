@@ -247,7 +247,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const int row0 = tile->row_block * kTileRows;
         for (int ks = 0; ks < k_steps; ++ks) {
           if (!mbar_wait(smem_u32(empty + stage), phase ^ 1, wait_limit)) {
-            atomicExch(status, kProducerWait);
+            atomicCAS(status, 0u, kProducerWait);
             ok = false;
             break;
           }
@@ -278,7 +278,9 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       int met = 0;
       if (lane == 0) {
         const volatile unsigned long long * cnt = item_done + tl->wait_item;
-        for (uint32_t i = 0; i < wait_limit; ++i) {
+        // a sixteenth of the budget of the barrier waits: when a dependency cannot be met this poll gives up first and
+        // its code (the first one recorded stays) names the cause; the roles waiting on this warp follow
+        for (uint32_t i = 0; i < max(wait_limit >> 4, 1u); ++i) {
           if (*cnt >= tl->wait_count + wait_extra) {
             met = 1;
             break;
@@ -307,7 +309,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const GemvTile * tl = tile_at(issue_ti);
         if (!dependency_met(tl, issue_ti == proc_ti)) {
           if (issue_ti == proc_ti) {
-            if (lane == 0) atomicExch(status, kDependencyWait);
+            if (lane == 0) atomicCAS(status, 0u, kDependencyWait);
             prep_ok = false;
           }
           break;
@@ -325,7 +327,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       if (!prep_ok) break;
       const GemvTile * tile = tile_at(proc_ti);
       if (x_raw_depth == 0 && !dependency_met(tile, true)) {
-        if (lane == 0) atomicExch(status, kDependencyWait);
+        if (lane == 0) atomicCAS(status, 0u, kDependencyWait);
         break;
       }
       const int buf = (x_bufs == 2) ? (xi & 1) : 0;
@@ -333,7 +335,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       const uint32_t rb = x_raw_depth > 0 ? xi % x_raw_depth : 0;
       if ((x_raw_depth > 0 && !mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1, wait_limit)) ||
           !mbar_wait(smem_u32(xempty + buf), xphase ^ 1, wait_limit)) {
-        if (lane == 0) atomicExch(status, kPrepWait);
+        if (lane == 0) atomicCAS(status, 0u, kPrepWait);
         break;
       }
       const int k = tile->k;
@@ -425,7 +427,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         prev_item = tile->item;
         buf = (x_bufs == 2) ? (xi & 1) : 0;
         if (!mbar_wait(smem_u32(xfull + buf), (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1), wait_limit)) {
-          if (lane == 0) atomicExch(status, kConsumerXWait);
+          if (lane == 0) atomicCAS(status, 0u, kConsumerXWait);
           ok = false;
           break;
         }
@@ -456,7 +458,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       }
       for (int ks = 0; ks < k_steps; ++ks) {
         if (!mbar_wait(smem_u32(full + stage), phase, wait_limit)) {
-          if (lane == 0) atomicExch(status, kConsumerWait);
+          if (lane == 0) atomicCAS(status, 0u, kConsumerWait);
           ok = false;
           break;
         }
@@ -512,7 +514,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       float * slot = red + ((rb * kRowGroups + rg) * 32 + lane) * 4 * MT;
       if (kh == 1) {
         if (!mbar_wait(smem_u32(red_free + rb), rphase ^ 1, wait_limit)) {
-          if (lane == 0) atomicExch(status, kConsumerWait);
+          if (lane == 0) atomicCAS(status, 0u, kConsumerWait);
           ok = false;
           break;
         }
@@ -523,7 +525,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         if (lane == 0) mbar_arrive(smem_u32(red_full + rb));
       } else {
         if (!mbar_wait(smem_u32(red_full + rb), rphase, wait_limit)) {
-          if (lane == 0) atomicExch(status, kConsumerWait);
+          if (lane == 0) atomicCAS(status, 0u, kConsumerWait);
           ok = false;
           break;
         }
