@@ -52,8 +52,10 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxRawDepth = 4;
 constexpr int kZeroHalfs = 320;                 // covers the 8 chunk offsets (32 halfs apart) of a K step + a bank shift
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr int kXPad = 16;                       // fp16 elements of padding between tokens: consecutive tokens sit 32 bytes
-                                                // apart modulo the 128-byte bank window, so a B-fragment load has no conflict
+// fp16 elements of padding between tokens.  Up to four tokens: consecutive tokens sit 32 bytes apart modulo the
+// 128-byte bank window; five to eight tokens (the dense mapping below): 64 bytes apart, because there the eight lanes
+// served together by a 128-bit load read 64 contiguous bytes of each of two tokens.
+__host__ __device__ constexpr int x_pad(int m_tokens) { return m_tokens > 4 ? 32 : 16; }
 
 enum Epilogue : int { kEpiPlain = 0, kEpiGateUp = 1 };
 
@@ -160,6 +162,13 @@ __device__ __forceinline__ void mma_f16_acc(float (&c)[4], uint32_t a0, uint32_t
     "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Product of two fp16x2 registers.
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 
 // Unsigned E4M3 byte (bit 7 clear) -> fp32 (0x7f = 480, subnormals exact): the byte placed at bit 20 is the
@@ -339,7 +348,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         break;
       }
       const int k = tile->k;
-      const int xstride = k + kXPad;
+      const int xstride = k + x_pad(m_tokens);
       const __nv_bfloat16 * x = x_raw_depth > 0
                                   ? reinterpret_cast<const __nv_bfloat16 *>(xraw + static_cast<size_t>(rb) * x_raw_bytes)
                                   : (x_override != nullptr ? x_override : tile->x);
@@ -397,6 +406,11 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     const bool b_owner = (t >> 1) == hB;
     // D role: this lane receives block half hD = t >> 1, tokens 2*(t&1), 2*(t&1)+1 for rows g and g+8.
     const int hD = t >> 1;
+    // Dense mapping (five to eight tokens): byte selectors that pull the scale of this lane's block (block
+    // 2*cq + hD of a 4-block scale word) into both halves of a register.
+    constexpr bool kDense = (MT == 2);
+    const uint32_t dense_sel[2] = {0x4040u | (static_cast<uint32_t>(hD) * 0x0101u),
+                                   0x4040u | (static_cast<uint32_t>(2 + hD) * 0x0101u)};
     // ldmatrix row address of this lane: matrix mi = lane >> 3 -> rows 8*(mi&1).., chunk offset mi >> 1
     const int lm_row = 16 * rg + 8 * ((lane >> 3) & 1) + (lane & 7);
     const int lm_chunk = lane >> 4;
@@ -435,7 +449,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         ++xi;
       }
       const int k_steps = tile->k_steps;
-      const int xstride = tile->k + kXPad;
+      const int xstride = tile->k + x_pad(m_tokens);
       const __half * xb = xbuf + buf * x_buf_halfs;
       const float * xs = xsbuf + buf * xs_buf_floats;
 
@@ -449,12 +463,21 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       // that MMA column, else a zeroed region (same offsets work in both, so the inner loop has no predicates).
       const __half * bsrc[MT];
       int bstep[MT];
+      if constexpr (kDense) {
+        // dense mapping: MMA column g is token g; this lane feeds the k-slots of its own eight codes of a chunk
+        const bool owner = g < m_tokens;
+        bsrc[0] = owner ? xb + static_cast<size_t>(g) * xstride + 8 * t : zeros;
+        bstep[0] = owner ? 256 : 0;
+        bsrc[1] = bsrc[0];
+        bstep[1] = 0;
+      } else {
 #pragma unroll
-      for (int ts = 0; ts < MT; ++ts) {
-        const int token = 4 * ts + mB;
-        const bool owner = b_owner && token < m_tokens;
-        bsrc[ts] = owner ? xb + static_cast<size_t>(token) * xstride + x_lane_off : zsrc;
-        bstep[ts] = owner ? 256 : 0;
+        for (int ts = 0; ts < MT; ++ts) {
+          const int token = 4 * ts + mB;
+          const bool owner = b_owner && token < m_tokens;
+          bsrc[ts] = owner ? xb + static_cast<size_t>(token) * xstride + x_lane_off : zsrc;
+          bstep[ts] = owner ? 256 : 0;
+        }
       }
       for (int ks = 0; ks < k_steps; ++ks) {
         if (!mbar_wait(smem_u32(full + stage), phase, wait_limit)) {
@@ -471,6 +494,32 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           const int pair = 2 * kh + pp;
           uint32_t r[4];
           ldmatrix_x4(codes_addr + (((2 * pair + lm_chunk) ^ lm_xor) << 4), r[0], r[1], r[2], r[3]);
+          if constexpr (kDense) {
+            // Five to eight tokens: the eight MMA columns are the tokens, every k-slot is used, and the chunk's two
+            // blocks (quad threads 0,1 and 2,3) share one MMA.  Their block scales therefore go into the A operand:
+            // E2M1 x E4M3 is exact in fp16 (the scale byte at bit 7 of an fp16 is the scale times 2^-8, 0x7f = 480
+            // included; products down to 2^-18 are fp16 subnormals, which multiply and MMA handle exactly), and
+            // the MMAs accumulate straight over K in fp32.  The 2^8 is undone in the epilogue.
+            const uint32_t sw0 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off0);        // row r0, 4 blocks
+            const uint32_t sw1 = *reinterpret_cast<const uint32_t *>(sc + pair * 512 + sc_off0 + 128);  // row r0 + 8
+#pragma unroll
+            for (int cq = 0; cq < 2; ++cq) {
+              const int q = 2 * pair + cq;
+              uint32_t a_lo[4], a_hi[4];
+              e2m1x8_to_f16(r[2 * cq], a_lo);
+              e2m1x8_to_f16(r[2 * cq + 1], a_hi);
+              const uint32_t s0 = __byte_perm(sw0, 0u, dense_sel[cq]) << 7;  // (scale, scale) as fp16x2, times 2^-8
+              const uint32_t s1 = __byte_perm(sw1, 0u, dense_sel[cq]) << 7;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                a_lo[i] = hmul2_bits(a_lo[i], s0);
+                a_hi[i] = hmul2_bits(a_hi[i], s1);
+              }
+              const uint4 b = *reinterpret_cast<const uint4 *>(bsrc[0] + 32 * q);
+              mma_f16_acc(acc[cq], a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
+              mma_f16_acc(acc[cq], a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
+            }
+          } else {
           // scale bytes of this pair's 4-block tile (blocks 4*pair .. 4*pair+3 of rows r0 and r0+8): plain byte
           // loads keep the integer pipe free for the FP4 conversions
           const uint8_t * sc0 = sc + pair * 512 + sc_off0 + hD;
@@ -495,6 +544,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
               acc[ts][3] = fmaf(c[3], s1, acc[ts][3]);
             }
           }
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + stage));
@@ -506,6 +556,12 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         for (int ts = 0; ts < MT; ++ts) bsrc[ts] += bstep[ts];
       }
       if (!ok) break;
+      if constexpr (kDense) {
+        // the two MMA chains (even and odd chunks) hold partial sums of the same outputs
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[0][i] += acc[1][i];
+      }
+      constexpr int kGroups = kDense ? 1 : MT;  // float4 groups of sums a lane carries into the epilogue
 
       // Meet the partner warp's half-K sums in shared memory (double-buffered by tile parity): the kh = 1 warp
       // writes, the kh = 0 warp adds, combines the two block halves (lanes t and t^2) and stores.
@@ -519,7 +575,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           break;
         }
 #pragma unroll
-        for (int ts = 0; ts < MT; ++ts)
+        for (int ts = 0; ts < kGroups; ++ts)
           *reinterpret_cast<float4 *>(slot + 4 * ts) = make_float4(acc[ts][0], acc[ts][1], acc[ts][2], acc[ts][3]);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(red_full + rb));
@@ -530,7 +586,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           break;
         }
 #pragma unroll
-        for (int ts = 0; ts < MT; ++ts) {
+        for (int ts = 0; ts < kGroups; ++ts) {
           const float4 o = *reinterpret_cast<const float4 *>(slot + 4 * ts);
           acc[ts][0] += o.x;
           acc[ts][1] += o.y;
@@ -547,15 +603,19 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const bool gate_up = tile->epilogue == kEpiGateUp;
         const float s2_up = tile->s2_up;
 #pragma unroll
-        for (int ts = 0; ts < MT; ++ts) {
+        for (int ts = 0; ts < kGroups; ++ts) {
+          if constexpr (!kDense) {
+            // the two block halves of a chunk sit in lanes t and t ^ 2
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc[ts][i] += __shfl_xor_sync(0xffffffffu, acc[ts][i], 2);
-          if (t < 2) {
-            const int tok0 = 4 * ts + 2 * t;
+            for (int i = 0; i < 4; ++i) acc[ts][i] += __shfl_xor_sync(0xffffffffu, acc[ts][i], 2);
+          }
+          if (kDense || t < 2) {
+            // dense: this lane holds tokens 2t, 2t+1 of rows r0 and r0 + 8, with the block scales' 2^-8 still in
+            const int tok0 = kDense ? 2 * t : 4 * ts + 2 * t;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               if (tok0 + e < m_tokens) {
-                const float unscale = xs[tok0 + e];  // undoes the token's fp16 scaling
+                const float unscale = xs[tok0 + e] * (kDense ? 256.0f : 1.0f);  // undoes the token's fp16 scaling
                 if (gate_up) {
                   // rows alternate 8 gate / 8 up: this lane's row r0 is gate row j, its row r0 + 8 the matching up row
                   const int j = (row_a >> 4) * 8 + (row_a & 7);
@@ -625,15 +685,20 @@ struct Plan {
 // Shared-memory plan for a batch with at most max_k columns: two activation buffers, then as many ring stages as fit.
 bool make_plan(int m, int max_k, Plan * p) {
   const int mt = m <= 4 ? 1 : 2;
-  const int x_halfs = ((m * (max_k + kXPad) + 63) / 64) * 64;  // whole 128-byte bank spans
+  const int x_halfs = ((m * (max_k + x_pad(m)) + 63) / 64) * 64;  // whole 128-byte bank spans
   const int xs_floats = 8;
   const int raw_bytes = ((m * max_k * 2 + 127) / 128) * 128;
   const int base = 1024 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
                    kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
   // Prefer two fp16 activation buffers and a deep raw-activation ring; give those up (one buffer, shallower ring)
   // before giving up ring stages below 4.
+#ifdef Q35B_PLAN_BUFS
+  for (int bufs = Q35B_PLAN_BUFS; bufs >= 1; --bufs) {
+    for (int depth = Q35B_PLAN_DEPTH; depth >= 0; --depth) {
+#else
   for (int bufs = 2; bufs >= 1; --bufs) {
     for (int depth = (bufs == 2 ? kMaxRawDepth : 2); depth >= (bufs == 2 ? 1 : 0); --depth) {
+#endif
       const int fixed = base + bufs * x_halfs * 2 + depth * raw_bytes;
       const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
       if (stages >= 4 || (bufs == 1 && depth == 0 && stages >= 3)) {

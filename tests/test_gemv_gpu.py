@@ -68,6 +68,32 @@ def test_all_codes_and_scale_bytes(engine, oracle):
     assert oracle.rel_l2(oracle.bf16_to_f32(yb), oracle.bf16_to_f32(eb)) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("m", [1, 4, 5, 8])
+def test_every_unsigned_scale_byte_through_the_streaming_kernel(engine, oracle, m):
+    """All 128 unsigned E4M3 bytes (zero, the subnormals 0x01..0x07, 0x7f = 480) as block scales of the streaming
+    kernel, which for five to eight tokens folds the scale into its fp16 operand: every block's byte is its index
+    modulo 128, so each row meets every byte, with every E2M1 code around it."""
+    rng = np.random.default_rng(m)
+    n, k = 384, 2048
+    codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    scales = ((np.arange(n)[:, None] * 5 + np.arange(k // 16)[None, :]) % 128).astype(np.uint8)
+    s2 = 1.0 / 4096
+    xb = make_activations(m, k, 30 + m, outlier_frac=0.002)
+    w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+    yb = from_torch_bf16(engine.gemv_w4a16(w, to_torch_bf16(xb), kernel=engine.GEMV_STREAM))
+    eb, _ = oracle.gemv_bf16(codes, scales, s2, xb, threads=8)
+    assert oracle.rel_l2(oracle.bf16_to_f32(yb), oracle.bf16_to_f32(eb)) <= REL_L2_TOL
+    # blocks whose scale is a subnormal or zero only: the small products must not be flushed
+    tiny = scales.copy()
+    tiny[:] = (np.arange(n)[:, None] + np.arange(k // 16)[None, :]) % 8
+    w2 = engine.Nvfp4Weight.from_host(codes, tiny, 1.0)
+    yb2 = from_torch_bf16(engine.gemv_w4a16(w2, to_torch_bf16(xb), kernel=engine.GEMV_STREAM))
+    eb2, _ = oracle.gemv_bf16(codes, tiny, 1.0, xb, threads=8)
+    assert oracle.rel_l2(oracle.bf16_to_f32(yb2), oracle.bf16_to_f32(eb2)) <= REL_L2_TOL
+    w.close()
+    w2.close()
+
+
 def test_f32_contract_of_reference_benchmark(engine, oracle):
     """fp32 input x[i] = ((i%17)-8)/17 scaled by input_scale, fp32 output: the reference bench's check
     (src/runtime/cuda_bench.cu:2085-2100) on its first 64 rows, max_abs_error style."""
