@@ -55,7 +55,15 @@ constexpr uint32_t kWaitLimit = 1u << 22;
 // fp16 elements of padding between tokens.  Up to four tokens: consecutive tokens sit 32 bytes apart modulo the
 // 128-byte bank window; five to eight tokens (the dense mapping below): 64 bytes apart, because there the eight lanes
 // served together by a 128-bit load read 64 contiguous bytes of each of two tokens.
-__host__ __device__ constexpr int x_pad(int m_tokens) { return m_tokens > 4 ? 32 : 16; }
+#ifndef Q35B_COOP_FROM
+#define Q35B_COOP_FROM 5
+#endif
+constexpr int kCoopFrom = Q35B_COOP_FROM;  // token count from which the consumer warps convert the activations themselves
+#ifndef Q35B_DENSE_FROM
+#define Q35B_DENSE_FROM 5
+#endif
+constexpr int kDenseFrom = Q35B_DENSE_FROM;  // token count from which the dense MMA mapping (template MT = 2) is used
+__host__ __device__ constexpr int x_pad(int m_tokens) { return m_tokens >= kDenseFrom ? 32 : 16; }
 
 enum Epilogue : int { kEpiPlain = 0, kEpiGateUp = 1 };
 
@@ -185,6 +193,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
                          __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
                          int x_raw_bytes, int x_raw_depth, int x_bufs, unsigned long long * item_done,
                          int counted_items, unsigned int * status, uint32_t wait_limit, unsigned int wait_extra) {
+  constexpr bool kDense = (MT == 2);  // five to eight tokens: dense MMA mapping, activations converted by the consumers
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled code tiles; pointer arithmetic on the __shared__ array (rather than an
   // integer round trip) keeps every later access a shared-memory access for the compiler.
@@ -204,6 +213,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   uint64_t * red_full = xempty + 2;
   uint64_t * red_free = red_full + 2;
   uint64_t * xraw_full = red_free + 2;
+  uint64_t * conv = xraw_full + kMaxRawDepth;                                      // dense path: amax known, conversion done
+  uint32_t * amax_s = reinterpret_cast<uint32_t *>(conv + 2);                      // [2][8] per-token amax bits, by item parity
 
   // Programmatic dependent launch: the next kernel of the stream may start on an SM as soon as this kernel's CTA has
   // left it, and this kernel may start under the tail of the previous one.  Weights, tile descriptors and tensor
@@ -228,6 +239,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       mbar_init(smem_u32(red_free + i), kRowGroups);
     }
     for (int i = 0; i < x_raw_depth; ++i) mbar_init(smem_u32(xraw_full + i), 1);
+    for (int i = 0; i < 2; ++i) mbar_init(smem_u32(conv + i), kConsumerWarps);
+    for (int i = 0; i < 16; ++i) amax_s[i] = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // stage this CTA's tile descriptors; clear the zero region
@@ -347,6 +360,25 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         if (lane == 0) atomicCAS(status, 0u, kPrepWait);
         break;
       }
+      if (kDense || m_tokens >= kCoopFrom) {
+        // Cooperative conversion: the raw BF16 rows go straight into the (padded) buffer the consumers will read; the sixteen
+        // consumer warps convert them in place when they reach the item.  One warp converting eight tokens takes
+        // several microseconds per item, and a CTA changes item at almost every tile of a 4B-class step.
+        if (lane == 0) {
+          const int k = tile->k;
+          const uint32_t bar = smem_u32(xfull + buf);
+          const __nv_bfloat16 * x = x_override != nullptr ? x_override : tile->x;
+          __half * xb = xbuf + buf * x_buf_halfs;
+          mbar_expect_tx(bar, static_cast<uint32_t>(m_tokens) * k * 2u);
+          for (int token = 0; token < m_tokens; ++token) {
+            bulk_load(smem_u32(xb + static_cast<size_t>(token) * (k + x_pad(m_tokens))), x + static_cast<size_t>(token) * k,
+                      static_cast<uint32_t>(k) * 2u, bar);
+          }
+        }
+        ++xi;
+        proc_ti = next_run(proc_ti + 1, tile->item);
+        continue;
+      }
       const int k = tile->k;
       const int xstride = k + x_pad(m_tokens);
       const __nv_bfloat16 * x = x_raw_depth > 0
@@ -408,7 +440,6 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
     const int hD = t >> 1;
     // Dense mapping (five to eight tokens): byte selectors that pull the scale of this lane's block (block
     // 2*cq + hD of a 4-block scale word) into both halves of a register.
-    constexpr bool kDense = (MT == 2);
     const uint32_t dense_sel[2] = {0x4040u | (static_cast<uint32_t>(hD) * 0x0101u),
                                    0x4040u | (static_cast<uint32_t>(2 + hD) * 0x0101u)};
     // ldmatrix row address of this lane: matrix mi = lane >> 3 -> rows 8*(mi&1).., chunk offset mi >> 1
@@ -435,6 +466,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       const GemvTile * tile = tile_at(ti);
       if (tile->item != prev_item) {
         if (prev_item >= 0) {
+          if (kDense || m_tokens >= kCoopFrom) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // a bulk copy overwrites what this warp converted
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(xempty + buf));
         }
@@ -446,6 +478,69 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           break;
         }
         if (xi == 0) asm volatile("griddepcontrol.wait;" ::: "memory");  // returns at once: the activation warp has waited
+        if (kDense || m_tokens >= kCoopFrom) {
+          // The raw BF16 rows of this item have landed in the buffer: the sixteen consumer warps turn them into
+          // scaled fp16 in place.  With T = 1, 2, 4 or 8 token slots (the power of two that holds the tokens), warp
+          // cw takes token cw % T and slice cw / T of its columns; the warps of a token agree on its amax through
+          // shared memory.  Both meeting points are bounded mbarrier waits.
+          const int tshift = m_tokens > 4 ? 3 : (m_tokens > 2 ? 2 : (m_tokens > 1 ? 1 : 0));
+          const int ctoken = cw & ((1 << tshift) - 1);
+          const int khalf = tile->k >> (4 - tshift);  // columns per slice
+          const bool live = ctoken < m_tokens;
+          __half * crow = xbuf + buf * x_buf_halfs + static_cast<size_t>(ctoken) * (tile->k + x_pad(m_tokens)) + (cw >> tshift) * khalf;
+          const uint32_t par = xi & 1;
+          uint32_t amax_bits = 0;
+          if (live) {
+            for (int i = lane * 8; i < khalf; i += 256) {
+              const uint4 q = *reinterpret_cast<const uint4 *>(crow + i);
+              const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                amax_bits = max(amax_bits, (r[j] << 16) & 0x7fffffffu);
+                amax_bits = max(amax_bits, r[j] & 0x7fff0000u);
+              }
+            }
+          }
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, off));
+          if (lane == 0) {
+            if (live) atomicMax(amax_s + par * 8 + ctoken, amax_bits);
+            mbar_arrive(smem_u32(conv + 0));
+          }
+          if (!mbar_wait(smem_u32(conv + 0), par, wait_limit)) {
+            if (lane == 0) atomicCAS(status, 0u, kConsumerXWait);
+            ok = false;
+            break;
+          }
+          if (live) {
+            // exact power-of-two scale putting the token's amax in [2^14, 2^15) (exponent field clamped to stay normal):
+            // fp16 then holds every BF16 significand exactly down to 2^-28 of the amax
+            int e = static_cast<int>(amax_s[par * 8 + ctoken] >> 23);
+            e = min(max(e, 16), 254);
+            const float scale = __uint_as_float(static_cast<uint32_t>(268 - e) << 23);
+            for (int i = lane * 8; i < khalf; i += 256) {
+              const uint4 q = *reinterpret_cast<const uint4 *>(crow + i);
+              const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+              uint32_t out[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __half2 h = __floats2half2_rn(__uint_as_float(r[j] << 16) * scale, __uint_as_float(r[j] & 0xffff0000u) * scale);
+                out[j] = *reinterpret_cast<const uint32_t *>(&h);
+              }
+              *reinterpret_cast<uint4 *>(crow + i) = make_uint4(out[0], out[1], out[2], out[3]);
+            }
+            if ((cw >> tshift) == 0 && lane == 0) (xsbuf + buf * xs_buf_floats)[ctoken] = __uint_as_float(static_cast<uint32_t>(e - 14) << 23);
+          }
+          // the words of the other parity serve the next item: nobody reads them any more, nobody adds to them yet
+          if (cw == 0 && lane < 8) amax_s[(par ^ 1) * 8 + lane] = 0u;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(conv + 1));
+          if (!mbar_wait(smem_u32(conv + 1), par, wait_limit)) {
+            if (lane == 0) atomicCAS(status, 0u, kConsumerXWait);
+            ok = false;
+            break;
+          }
+        }
         ++xi;
       }
       const int k_steps = tile->k_steps;
@@ -670,7 +765,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
 }
 
 constexpr int kSmemBudget = 227 * 1024;
-constexpr int kBarrierBytes = (2 * kMaxStages + 8 + kMaxRawDepth) * 8;
+constexpr int kBarrierBytes = (2 * kMaxStages + 8 + kMaxRawDepth + 2) * 8 + 2 * 8 * 4;
 
 struct Plan {
   int stages = 0;
@@ -684,12 +779,31 @@ struct Plan {
 
 // Shared-memory plan for a batch with at most max_k columns: two activation buffers, then as many ring stages as fit.
 bool make_plan(int m, int max_k, Plan * p) {
-  const int mt = m <= 4 ? 1 : 2;
+  const int mt = m < kDenseFrom ? 1 : 2;
   const int x_halfs = ((m * (max_k + x_pad(m)) + 63) / 64) * 64;  // whole 128-byte bank spans
   const int xs_floats = 8;
   const int raw_bytes = ((m * max_k * 2 + 127) / 128) * 128;
   const int base = 1024 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
                    kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
+  if (mt == 2 || m >= kCoopFrom) {
+    // Cooperative conversion: the raw rows are copied straight into the buffer the consumers convert in place, so there is no
+    // raw ring; two buffers (the next item's copy runs under the current item's tiles) when five stages remain.
+    for (int bufs = 2; bufs >= 1; --bufs) {
+      const int fixed = base + bufs * x_halfs * 2;
+      const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
+      if (stages >= (bufs == 2 ? 5 : 3)) {
+        p->stages = stages;
+        p->x_buf_halfs = x_halfs;
+        p->xs_buf_floats = xs_floats;
+        p->x_raw_bytes = 0;
+        p->x_raw_depth = 0;
+        p->x_bufs = bufs;
+        p->smem_bytes = fixed + stages * kStageBytes;
+        return true;
+      }
+    }
+    return false;
+  }
   // Prefer two fp16 activation buffers and a deep raw-activation ring; give those up (one buffer, shallower ring)
   // before giving up ring stages below 4.
 #ifdef Q35B_PLAN_BUFS
@@ -940,7 +1054,7 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   const GemvTile * d_tiles = b->tiles;
   const int * d_begin = b->cta_begin;
   const Plan & pl = b->plan;
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, b->m <= 4 ? gemv_w4a16_stream_kernel<1> : gemv_w4a16_stream_kernel<2>, d_items,
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, b->m < kDenseFrom ? gemv_w4a16_stream_kernel<1> : gemv_w4a16_stream_kernel<2>, d_items,
                                             d_tiles, d_begin, b->m, xo, yo, pl.stages, pl.x_buf_halfs, pl.xs_buf_floats,
                                             pl.x_raw_bytes, pl.x_raw_depth, pl.x_bufs, b->item_done, counted, b->status, b->wait_limit,
                                             b->wait_extra);
