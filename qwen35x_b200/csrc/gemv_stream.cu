@@ -21,10 +21,12 @@
 // 32-code chunk, token m<4), so one MMA pair yields, in each lane, the dot
 // product of exactly the block that lane loaded: no cross-lane data movement.
 // The E4M3 block scale multiplies that block dot in fp32 and accumulates.
-// Activations are converted BF16 -> fp16 per token with an exact power-of-two
-// scale taken from the token's amax, by a dedicated warp that prefetches the raw
-// activations of the next projections and runs one projection ahead
-// (double-buffered), so the conversion is never waited on.
+// Five to eight tokens use a dense mapping instead: the eight MMA columns are the tokens, every k-slot is used,
+// and the block scales are folded exactly into the fp16 weight operand, so the MMAs accumulate straight over K.
+// Activations are converted BF16 -> fp16 per token with an exact power-of-two scale taken from the token's amax:
+// a dedicated warp bulk-copies the raw rows of the next projection into one of two buffers (under the tiles of the
+// projection before), and the sixteen consumer warps convert them in place when they get there, each a slice of
+// one token, meeting twice on bounded mbarriers (amax known, conversion done).
 //
 // All waits are bounded; on expiry a code is written to the batch's status word.
 #include <cuda_bf16.h>
@@ -46,23 +48,16 @@ constexpr int kScaleBytes = 4 * 512;
 constexpr int kStageBytes = kCodesBytes + kScaleBytes;
 constexpr int kRowGroups = 8;                   // 16-row groups per tile
 constexpr int kConsumerWarps = 16;              // each row group is shared by two warps that split the K step
-constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 activation prep, 16 consumers
+constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 activation copies, 16 consumers
 constexpr int kMaxTilesInSmem = 64;             // tile descriptors staged per CTA
 constexpr int kMaxStages = 8;
-constexpr int kMaxRawDepth = 4;
 constexpr int kZeroHalfs = 320;                 // covers the 8 chunk offsets (32 halfs apart) of a K step + a bank shift
 constexpr uint32_t kWaitLimit = 1u << 22;
 // fp16 elements of padding between tokens.  Up to four tokens: consecutive tokens sit 32 bytes apart modulo the
 // 128-byte bank window; five to eight tokens (the dense mapping below): 64 bytes apart, because there the eight lanes
 // served together by a 128-bit load read 64 contiguous bytes of each of two tokens.
-#ifndef Q35B_COOP_FROM
-#define Q35B_COOP_FROM 5
-#endif
-constexpr int kCoopFrom = Q35B_COOP_FROM;  // token count from which the consumer warps convert the activations themselves
-#ifndef Q35B_DENSE_FROM
-#define Q35B_DENSE_FROM 5
-#endif
-constexpr int kDenseFrom = Q35B_DENSE_FROM;  // token count from which the dense MMA mapping (template MT = 2) is used
+constexpr int kDenseFrom = 5;  // token count from which the dense MMA mapping (template MT = 2) is used; measured: with
+                               // two to four tokens the (block, token) mapping is 4-7 % faster
 __host__ __device__ constexpr int x_pad(int m_tokens) { return m_tokens >= kDenseFrom ? 32 : 16; }
 
 enum Epilogue : int { kEpiPlain = 0, kEpiGateUp = 1 };
@@ -191,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * __restrict__ tiles,
                          const int * __restrict__ cta_begin, int m_tokens, const __nv_bfloat16 * x_override,
                          __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
-                         int x_raw_bytes, int x_raw_depth, int x_bufs, unsigned long long * item_done,
+                         int x_bufs, unsigned long long * item_done,
                          int counted_items, unsigned int * status, uint32_t wait_limit, unsigned int wait_extra) {
   constexpr bool kDense = (MT == 2);  // five to eight tokens: dense MMA mapping, activations converted by the consumers
   extern __shared__ uint8_t smem_raw[];
@@ -203,17 +198,15 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   float * xsbuf = reinterpret_cast<float *>(zeros + kZeroHalfs);                   // 2 buffers of xs_buf_floats (1/scale)
   float * red = xsbuf + 2 * xs_buf_floats;                                         // 2 x [8 row groups][32 lanes][4*MT]
   GemvTile * stile = reinterpret_cast<GemvTile *>(red + 2 * kRowGroups * 32 * 4 * MT);
-  uint8_t * xraw = reinterpret_cast<uint8_t *>(stile + kMaxTilesInSmem);           // x_raw_depth buffers of x_raw_bytes
-  uint64_t * bars = reinterpret_cast<uint64_t *>(xraw + static_cast<size_t>(x_raw_depth) * x_raw_bytes);
-  // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2], red_full[2], red_free[2], xraw_full[kMaxRawDepth]
+  uint64_t * bars = reinterpret_cast<uint64_t *>(stile + kMaxTilesInSmem);
+  // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2], red_full[2], red_free[2], conv[2]
   uint64_t * full = bars;
   uint64_t * empty = bars + kMaxStages;
   uint64_t * xfull = bars + 2 * kMaxStages;
   uint64_t * xempty = xfull + 2;
   uint64_t * red_full = xempty + 2;
   uint64_t * red_free = red_full + 2;
-  uint64_t * xraw_full = red_free + 2;
-  uint64_t * conv = xraw_full + kMaxRawDepth;                                      // dense path: amax known, conversion done
+  uint64_t * conv = red_free + 2;                                                  // consumers: amax known, conversion done
   uint32_t * amax_s = reinterpret_cast<uint32_t *>(conv + 2);                      // [2][8] per-token amax bits, by item parity
 
   // Programmatic dependent launch: the next kernel of the stream may start on an SM as soon as this kernel's CTA has
@@ -238,7 +231,6 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       mbar_init(smem_u32(red_full + i), kRowGroups);
       mbar_init(smem_u32(red_free + i), kRowGroups);
     }
-    for (int i = 0; i < x_raw_depth; ++i) mbar_init(smem_u32(xraw_full + i), 1);
     for (int i = 0; i < 2; ++i) mbar_init(smem_u32(conv + i), kConsumerWarps);
     for (int i = 0; i < 16; ++i) amax_s[i] = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -286,15 +278,15 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ activation prep (BF16 -> scaled fp16)
-    // Raw BF16 activations of the next projections are bulk-copied into a small ring ahead of time (so no global
-    // latency is ever waited on here), then converted into one of the two fp16 buffers the consumers read.
+    // ------------------------------------------------------------ activation copies
+    // Bulk-copies the raw BF16 activations of the next projection into one of the (one or two) activation buffers,
+    // token rows padded apart; the consumers convert them to scaled fp16 in place.
     auto next_run = [&](int ti, int prev) {  // first tile index >= ti whose projection differs from `prev`
       while (ti < n_tiles && tile_at(ti)->item == prev) ++ti;
       return ti;
     };
     // An item that runs after another one may read its activations only when every storing warp of every tile of
-    // that item has counted itself in item_done (stores fenced before the count).  `block` false: just look.
+    // that item has counted itself in item_done (stores fenced before the count).
     auto dependency_met = [&](const GemvTile * tl, bool block) -> bool {
       if (tl->wait_item < 0) return true;
       int met = 0;
@@ -319,109 +311,35 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       return met != 0;
     };
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    int issue_ti = next_run(0, -1);
-    uint32_t issued = 0;
-    int proc_ti = issue_ti;
+    int proc_ti = next_run(0, -1);
     uint32_t xi = 0;
-    bool prep_ok = true;
-    while (proc_ti < n_tiles && prep_ok) {
-      // keep up to x_raw_depth raw copies in flight (none when the plan has no room for a raw ring); a copy whose
-      // source is not complete yet is not issued ahead of time, only when its turn to be converted has come
-      while (x_raw_depth > 0 && issue_ti < n_tiles && issued < xi + static_cast<uint32_t>(x_raw_depth)) {
-        const GemvTile * tl = tile_at(issue_ti);
-        if (!dependency_met(tl, issue_ti == proc_ti)) {
-          if (issue_ti == proc_ti) {
-            if (lane == 0) atomicCAS(status, 0u, kDependencyWait);
-            prep_ok = false;
-          }
-          break;
-        }
-        if (lane == 0) {
-          const uint32_t rb = issued % x_raw_depth;
-          const uint32_t bytes = static_cast<uint32_t>(m_tokens) * tl->k * 2u;
-          const __nv_bfloat16 * x = x_override != nullptr ? x_override : tl->x;
-          mbar_expect_tx(smem_u32(xraw_full + rb), bytes);
-          bulk_load(smem_u32(xraw + static_cast<size_t>(rb) * x_raw_bytes), x, bytes, smem_u32(xraw_full + rb));
-        }
-        ++issued;
-        issue_ti = next_run(issue_ti + 1, tl->item);
-      }
-      if (!prep_ok) break;
+    while (proc_ti < n_tiles) {
+      // The raw BF16 rows of the next projection go straight into the (padded) buffer the consumers will read; the
+      // sixteen consumer warps convert them in place when they reach the item.  (One warp converting eight tokens
+      // takes several microseconds per item, and a CTA changes item at almost every tile of a 4B-class step.)
+      // With two buffers the copy runs under the tiles of the item before.
       const GemvTile * tile = tile_at(proc_ti);
-      if (x_raw_depth == 0 && !dependency_met(tile, true)) {
+      if (!dependency_met(tile, true)) {
         if (lane == 0) atomicCAS(status, 0u, kDependencyWait);
         break;
       }
       const int buf = (x_bufs == 2) ? (xi & 1) : 0;
       const uint32_t xphase = (x_bufs == 2) ? ((xi >> 1) & 1) : (xi & 1);
-      const uint32_t rb = x_raw_depth > 0 ? xi % x_raw_depth : 0;
-      if ((x_raw_depth > 0 && !mbar_wait(smem_u32(xraw_full + rb), (xi / x_raw_depth) & 1, wait_limit)) ||
-          !mbar_wait(smem_u32(xempty + buf), xphase ^ 1, wait_limit)) {
+      if (!mbar_wait(smem_u32(xempty + buf), xphase ^ 1, wait_limit)) {
         if (lane == 0) atomicCAS(status, 0u, kPrepWait);
         break;
       }
-      if (kDense || m_tokens >= kCoopFrom) {
-        // Cooperative conversion: the raw BF16 rows go straight into the (padded) buffer the consumers will read; the sixteen
-        // consumer warps convert them in place when they reach the item.  One warp converting eight tokens takes
-        // several microseconds per item, and a CTA changes item at almost every tile of a 4B-class step.
-        if (lane == 0) {
-          const int k = tile->k;
-          const uint32_t bar = smem_u32(xfull + buf);
-          const __nv_bfloat16 * x = x_override != nullptr ? x_override : tile->x;
-          __half * xb = xbuf + buf * x_buf_halfs;
-          mbar_expect_tx(bar, static_cast<uint32_t>(m_tokens) * k * 2u);
-          for (int token = 0; token < m_tokens; ++token) {
-            bulk_load(smem_u32(xb + static_cast<size_t>(token) * (k + x_pad(m_tokens))), x + static_cast<size_t>(token) * k,
-                      static_cast<uint32_t>(k) * 2u, bar);
-          }
+      if (lane == 0) {
+        const int k = tile->k;
+        const uint32_t bar = smem_u32(xfull + buf);
+        const __nv_bfloat16 * x = x_override != nullptr ? x_override : tile->x;
+        __half * xb = xbuf + buf * x_buf_halfs;
+        mbar_expect_tx(bar, static_cast<uint32_t>(m_tokens) * k * 2u);
+        for (int token = 0; token < m_tokens; ++token) {
+          bulk_load(smem_u32(xb + static_cast<size_t>(token) * (k + x_pad(m_tokens))), x + static_cast<size_t>(token) * k,
+                    static_cast<uint32_t>(k) * 2u, bar);
         }
-        ++xi;
-        proc_ti = next_run(proc_ti + 1, tile->item);
-        continue;
       }
-      const int k = tile->k;
-      const int xstride = k + x_pad(m_tokens);
-      const __nv_bfloat16 * x = x_raw_depth > 0
-                                  ? reinterpret_cast<const __nv_bfloat16 *>(xraw + static_cast<size_t>(rb) * x_raw_bytes)
-                                  : (x_override != nullptr ? x_override : tile->x);
-      __half * xb = xbuf + buf * x_buf_halfs;
-      float * xs = xsbuf + buf * xs_buf_floats;
-      for (int token = 0; token < m_tokens; ++token) {
-        const __nv_bfloat16 * xt = x + static_cast<size_t>(token) * k;
-        // exact power-of-two scale putting the token's amax in [2^14, 2^15) (exponent field clamped to stay normal):
-        // fp16 then holds every BF16 significand exactly down to 2^-28 of the amax
-        uint32_t amax_bits = 0;
-        for (int i = lane * 8; i < k; i += 256) {
-          const uint4 q = *reinterpret_cast<const uint4 *>(xt + i);
-          const uint32_t r[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            amax_bits = max(amax_bits, (r[j] << 16) & 0x7fffffffu);
-            amax_bits = max(amax_bits, r[j] & 0x7fff0000u);
-          }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, off));
-        int e = static_cast<int>(amax_bits >> 23);
-        e = min(max(e, 16), 254);
-        const float scale = __uint_as_float(static_cast<uint32_t>(268 - e) << 23);
-        const float inv_scale = __uint_as_float(static_cast<uint32_t>(e - 14) << 23);
-        __half * xo = xb + static_cast<size_t>(token) * xstride;
-        for (int i = lane * 8; i < k; i += 256) {
-          const uint4 q = *reinterpret_cast<const uint4 *>(xt + i);
-          const uint32_t r[4] = {q.x, q.y, q.z, q.w};
-          uint32_t out[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const __half2 h = __floats2half2_rn(__uint_as_float(r[j] << 16) * scale, __uint_as_float(r[j] & 0xffff0000u) * scale);
-            out[j] = *reinterpret_cast<const uint32_t *>(&h);
-          }
-          *reinterpret_cast<uint4 *>(xo + i) = make_uint4(out[0], out[1], out[2], out[3]);
-        }
-        if (lane == 0) xs[token] = inv_scale;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(xfull + buf));
       ++xi;
       proc_ti = next_run(proc_ti + 1, tile->item);
     }
@@ -466,7 +384,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       const GemvTile * tile = tile_at(ti);
       if (tile->item != prev_item) {
         if (prev_item >= 0) {
-          if (kDense || m_tokens >= kCoopFrom) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // a bulk copy overwrites what this warp converted
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // a bulk copy overwrites what this warp converted
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(xempty + buf));
         }
@@ -478,7 +396,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           break;
         }
         if (xi == 0) asm volatile("griddepcontrol.wait;" ::: "memory");  // returns at once: the activation warp has waited
-        if (kDense || m_tokens >= kCoopFrom) {
+        {
           // The raw BF16 rows of this item have landed in the buffer: the sixteen consumer warps turn them into
           // scaled fp16 in place.  With T = 1, 2, 4 or 8 token slots (the power of two that holds the tokens), warp
           // cw takes token cw % T and slice cw / T of its columns; the warps of a token agree on its amax through
@@ -765,66 +683,35 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
 }
 
 constexpr int kSmemBudget = 227 * 1024;
-constexpr int kBarrierBytes = (2 * kMaxStages + 8 + kMaxRawDepth + 2) * 8 + 2 * 8 * 4;
+constexpr int kBarrierBytes = (2 * kMaxStages + 8 + 2) * 8 + 2 * 8 * 4;
 
 struct Plan {
   int stages = 0;
   int x_buf_halfs = 0;
   int xs_buf_floats = 0;
-  int x_raw_bytes = 0;
-  int x_raw_depth = 0;
   int x_bufs = 0;
   int smem_bytes = 0;
 };
 
-// Shared-memory plan for a batch with at most max_k columns: two activation buffers, then as many ring stages as fit.
+// Shared-memory plan for a batch with at most max_k columns: activation buffers (raw BF16 rows land in them and are
+// converted in place, so there is no separate raw ring), then as many ring stages as fit.  Two buffers (the next
+// item's copy runs under the current item's tiles) when at least five stages remain, else one.
 bool make_plan(int m, int max_k, Plan * p) {
   const int mt = m < kDenseFrom ? 1 : 2;
   const int x_halfs = ((m * (max_k + x_pad(m)) + 63) / 64) * 64;  // whole 128-byte bank spans
   const int xs_floats = 8;
-  const int raw_bytes = ((m * max_k * 2 + 127) / 128) * 128;
   const int base = 1024 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
                    kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
-  if (mt == 2 || m >= kCoopFrom) {
-    // Cooperative conversion: the raw rows are copied straight into the buffer the consumers convert in place, so there is no
-    // raw ring; two buffers (the next item's copy runs under the current item's tiles) when five stages remain.
-    for (int bufs = 2; bufs >= 1; --bufs) {
-      const int fixed = base + bufs * x_halfs * 2;
-      const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
-      if (stages >= (bufs == 2 ? 5 : 3)) {
-        p->stages = stages;
-        p->x_buf_halfs = x_halfs;
-        p->xs_buf_floats = xs_floats;
-        p->x_raw_bytes = 0;
-        p->x_raw_depth = 0;
-        p->x_bufs = bufs;
-        p->smem_bytes = fixed + stages * kStageBytes;
-        return true;
-      }
-    }
-    return false;
-  }
-  // Prefer two fp16 activation buffers and a deep raw-activation ring; give those up (one buffer, shallower ring)
-  // before giving up ring stages below 4.
-#ifdef Q35B_PLAN_BUFS
-  for (int bufs = Q35B_PLAN_BUFS; bufs >= 1; --bufs) {
-    for (int depth = Q35B_PLAN_DEPTH; depth >= 0; --depth) {
-#else
   for (int bufs = 2; bufs >= 1; --bufs) {
-    for (int depth = (bufs == 2 ? kMaxRawDepth : 2); depth >= (bufs == 2 ? 1 : 0); --depth) {
-#endif
-      const int fixed = base + bufs * x_halfs * 2 + depth * raw_bytes;
-      const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
-      if (stages >= 4 || (bufs == 1 && depth == 0 && stages >= 3)) {
-        p->stages = stages;
-        p->x_buf_halfs = x_halfs;
-        p->xs_buf_floats = xs_floats;
-        p->x_raw_bytes = raw_bytes;
-        p->x_raw_depth = depth;
-        p->x_bufs = bufs;
-        p->smem_bytes = fixed + stages * kStageBytes;
-        return true;
-      }
+    const int fixed = base + bufs * x_halfs * 2;
+    const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
+    if (stages >= (bufs == 2 ? 5 : 3)) {
+      p->stages = stages;
+      p->x_buf_halfs = x_halfs;
+      p->xs_buf_floats = xs_floats;
+      p->x_bufs = bufs;
+      p->smem_bytes = fixed + stages * kStageBytes;
+      return true;
     }
   }
   return false;
@@ -1056,7 +943,7 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   const Plan & pl = b->plan;
   const cudaError_t le = cudaLaunchKernelEx(&cfg, b->m < kDenseFrom ? gemv_w4a16_stream_kernel<1> : gemv_w4a16_stream_kernel<2>, d_items,
                                             d_tiles, d_begin, b->m, xo, yo, pl.stages, pl.x_buf_halfs, pl.xs_buf_floats,
-                                            pl.x_raw_bytes, pl.x_raw_depth, pl.x_bufs, b->item_done, counted, b->status, b->wait_limit,
+                                            pl.x_bufs, b->item_done, counted, b->status, b->wait_limit,
                                             b->wait_extra);
   count_launch();
   Q35B_CUDA_TRY(le, "gemv_w4a16_stream_kernel launch");
