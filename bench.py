@@ -339,7 +339,8 @@ def run_engine(args, rank: int, world: int, local_rank: int) -> dict | None:
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
     achieved_graph = step_bytes / (ms_graph_step * 1e-3) / 1e9
-    traffic, traffic_source = ncu_traffic("decode_step_0p8b_m1") if args.m == 1 else (None, "no capture for this token count")
+    traffic, traffic_source = (ncu_traffic(f"decode_step_0p8b_m{args.m}") if args.m in (1, 8)
+                               else (None, "no capture for this token count"))
     out = {
         "metric": "nvfp4_decode_step_bandwidth", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
