@@ -992,6 +992,26 @@ def main() -> int:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.report and world > 1:
+        # the prefill cells with M >= 128, N-sharded over the ranks of this torchrun job
+        import torch
+        import torch.distributed as dist
+
+        import qwen35x_b200 as q
+        import shape_report
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        rep = shape_report.run_sharded(q, torch, dist, rank, world, torch.device("cuda", local_rank), peaks())
+        bad = [r for r in rep["sharded_prefill"] if not r["checked"]]
+        if rank == 0:
+            Path(args.report).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.report).write_text(json.dumps(rep, indent=1))
+            Path(args.report).with_suffix(".md").write_text(shape_report.sharded_to_markdown(rep))
+            print(json.dumps({"report": args.report, "gpus": world, "entries": len(rep["sharded_prefill"]), "failed_checks": len(bad)}))
+        dist.barrier()
+        dist.destroy_process_group()
+        return 3 if bad else 0
     if args.report:
         import torch
 

@@ -228,6 +228,107 @@ def gemm_entries(q, torch, device, peaks, n, k, ms, label, row_outliers=False):
     return out
 
 
+def sharded_gemm_entries(q, torch, dist, rank, world, device, peaks, n, k, ms, label, row_outliers=False):
+    """Prefill cells N-sharded over the ranks of a torchrun job (one process per GPU): every rank builds the same seeded
+    weight, keeps the rows q35b_shard_range gives it, quantises the replicated activations itself and computes its
+    columns.  Times are the maximum over ranks; TFLOP/s is the whole projection's FLOPs over that time.  The
+    exchange that would follow is not part of the cell (bench.py times it on the gate/up shape): its lower bound,
+    the bytes every rank takes in at the measured peer-copy rate, is printed beside the compute time."""
+    from qwen35x_b200 import sharding
+
+    out = []
+    stream = torch.cuda.Stream(device=device)
+    row_begin, row_count = sharding.shard_layout(n, world)[rank]
+    for m in ms:
+        gen = torch.Generator(device=device).manual_seed(7 + n + k + m)  # the same tensors on every rank
+        per_set = (n // world) * k * 9 // 16 + m * k * 9 // 16 + m * (n // world) * 2
+        sets = max(2, min(6, -(-int(1.3 * L2_BYTES) // per_set)))
+        data = []
+        checked = True
+        for i in range(sets):
+            codes, scales, s2 = _make_weight(q, torch, device, gen, n, k, row_outliers)
+            w = q.Nvfp4Weight.from_device(codes, scales, s2, shard_index=rank, shard_count=world)
+            x = torch.randn((m, k), generator=gen, device=device)
+            x[:, torch.randperm(k, generator=gen, device=device)[: max(1, -(-k // 1000))]] *= 20.0
+            x = x.to(torch.bfloat16)
+            scratch = q.act_scratch(m, k, device)
+            y = torch.empty((m, max(row_count, 1)), dtype=torch.bfloat16, device=device)
+            if row_count > 0:
+                q.project_prefill(w, x, out=y, scratch=scratch)
+            if i == 0 and row_count > 0:
+                torch.cuda.synchronize()
+                sl = slice(row_begin, row_begin + row_count)
+                checked = _check_gemm_rows(torch, w, codes[sl], scales[sl], s2, scratch[0].view(m, k // 2), scratch[1],
+                                           scratch[2], m, k, y)
+            del codes, scales
+            data.append((w, x, scratch, y))
+        torch.cuda.synchronize()
+
+        def gemm_only(d):
+            w, x, scratch, y = d
+            if row_count > 0:
+                q.gemm_w4a4(w, scratch[0].view(m, k // 2), scratch[1], scratch[2], m, out=y)
+
+        def quant_gemm(d):
+            w, x, scratch, y = d
+            if row_count > 0:
+                q.project_prefill(w, x, out=y, scratch=scratch)
+
+        flops = 2.0 * m * n * k
+        gather_in = m * (n - row_count) * 2
+        row = {"workload": label, "M": m, "N": n, "K": k, "GPUs": world, "rows_of_rank0": sharding.shard_layout(n, world)[0][1],
+               "GFLOP": round(flops / 1e9, 1),
+               "gather_us_at_peer_copy_rate": round(gather_in / 770e9 * 1e6, 1)}
+        for name, fn in (("gemm_only", gemm_only), ("quant_gemm", quant_gemm)):
+            graphs = [_capture(torch, stream, lambda d=d: fn(d)) for d in data]
+            dist.barrier()
+            us = _time_graphs(torch, stream, graphs, reps=sets * 2)
+            t = torch.tensor([us], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+            tf = flops / us / 1e6
+            row[name] = {"us": round(us, 2), "TFLOP/s": round(tf, 1),
+                         "fp4_nominal_frac": round(tf / (world * FP4_NOMINAL_TFLOPS), 4)}
+        ok = torch.tensor([1 if checked else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        row["checked"] = bool(ok.item())
+        out.append(row)
+        del data
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_sharded(q, torch, dist, rank, world, device, peaks) -> dict:
+    """The prefill cells with M >= 128 of the 4B-class prefill and of the sweep, N-sharded over `world` GPUs."""
+    report = {"peaks": peaks, "gpus": world, "sharded_prefill": []}
+    for (n, k) in ((18432, 2560), (2560, 9216)):
+        report["sharded_prefill"] += sharded_gemm_entries(q, torch, dist, rank, world, device, peaks, n, k, [512, 4096],
+                                                          "config 4: 4B-class prefill")
+    for (n, k) in ((3584, 1024), (9216, 2560), (2560, 9216), (32768, 2560)):
+        report["sharded_prefill"] += sharded_gemm_entries(q, torch, dist, rank, world, device, peaks, n, k, [128, 1024, 4096],
+                                                          "config 5 sweep (1% rows x8)", row_outliers=True)
+    return report
+
+
+def sharded_to_markdown(report: dict) -> str:
+    w = report["gpus"]
+    out = [f"# Per-shape throughput report, prefill cells N-sharded over {w} x B200", "",
+           f"Command: `python -m torch.distributed.run --nproc-per-node {w} --master-addr 127.0.0.1 bench.py --gpus {w} "
+           "--report <path>.json` (CUDA-graph replays over rotating operand sets, CUDA events, maximum over ranks; every "
+           "rank checks sampled rows of its shard against the CPU port). TFLOP/s = FLOPs of the whole projection / that "
+           f"time; fraction of {w} x 9000 TFLOP/s nominal dense FP4. Activations are replicated and quantised on every "
+           "rank. The exchange is not in these cells: the last column is what taking in the other ranks' BF16 columns "
+           "costs at the measured 770 GB/s peer-copy rate.", "",
+           "| workload | M | N | K | rows per rank | shard GEMM us (max) | TFLOP/s | of nominal | quantise+GEMM us | checked | "
+           "BF16 gather at peer-copy rate us |", "|---|---|---|---|---|---|---|---|---|---|---|"]
+    for r in report["sharded_prefill"]:
+        g, qg = r["gemm_only"], r["quant_gemm"]
+        out.append(f"| {r['workload']} | {r['M']} | {r['N']} | {r['K']} | {r['rows_of_rank0']} | {g['us']:.2f} | {g['TFLOP/s']:.1f} | "
+                   f"{g['fp4_nominal_frac']:.3f} | {qg['us']:.2f} | {'yes' if r['checked'] else 'NO'} | "
+                   f"{r['gather_us_at_peer_copy_rate']:.1f} |")
+    return "\n".join(out) + "\n"
+
+
 def mlp_entries(q, torch, device, peaks, hidden, inter, ms, label):
     """Prefill MLP block x -> down(silu(gate x) * up x) + residual: the chain with the gate/up GEMM writing BF16 and a
     separate quantise pass before the down projection, and the chain whose gate/up epilogue writes NVFP4 directly."""

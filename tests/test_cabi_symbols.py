@@ -87,3 +87,18 @@ def test_shape_report_renders_markdown():
                    "| gemm | 512 | 18432 | 2560 | 48.3 | 10.00 | 100.0 | 0.011 | 0.015 | - | 10.00 | - | `gemm_w4a4_2cta_kernel` |",
                    "| mlp | 4096 | 2560 | 9216 | 579.8 | 248.30 | 2335.1 | 205.40 | 2823.4 |", "| (3584, 1024, 1) | 39418 | 4600 | 16 | 1024 rows |"):
         assert needle in md, needle
+
+
+def test_sharded_shape_report_renders_markdown():
+    """The N-sharded report's table (no GPU): one row per cell with the maximum-over-ranks time and the gather bound."""
+    import shape_report
+
+    report = {"peaks": {"hbm_gbs": 6545.0, "bf16_tflops": 1699.0}, "gpus": 4, "sharded_prefill": [
+        {"workload": "cell", "M": 4096, "N": 18432, "K": 2560, "GPUs": 4, "rows_of_rank0": 4608, "GFLOP": 386.5,
+         "gather_us_at_peer_copy_rate": 147.1, "checked": True,
+         "gemm_only": {"us": 33.0, "TFLOP/s": 11712.0, "fp4_nominal_frac": 0.3253},
+         "quant_gemm": {"us": 55.0, "TFLOP/s": 7027.0, "fp4_nominal_frac": 0.1952}}]}
+    md = shape_report.sharded_to_markdown(report)
+    assert "N-sharded over 4 x B200" in md
+    assert "| cell | 4096 | 18432 | 2560 | 4608 | 33.00 | 11712.0 | 0.325 | 55.00 | yes | 147.1 |" in md
+
