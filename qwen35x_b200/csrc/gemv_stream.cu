@@ -12,8 +12,10 @@
 // into a shared-memory ring (mbarrier full/empty pairs), so each CTA keeps
 // (stages x 18 KB) in flight regardless of how its consumer warps are doing.
 //
-// Arithmetic (kept off the critical path): 16 consumer warps; a pair of warps
-// owns 16 rows of the tile, each taking half of the K step (their partial sums
+// Arithmetic (kept off the critical path): one consumer warp per 16 rows of the tile.  Two shapes of CTA: eight
+// consumer warps and half of an SM's shared memory, two CTAs per SM, so that one CTA's stalls (change of
+// projection, tile hand-over, epilogue) run under the other's arithmetic; or, when the activations need more room,
+// sixteen consumer warps in one CTA per SM, two per row group splitting every K step (their partial sums
 // meet in shared memory at the end of the tile).  ldmatrix pulls 8 E2M1 codes per lane per register,
 // cvt.rn.f16x2.e2m1x2 (the sm_100a FP4 converter) turns every byte into two
 // exact fp16 values, and mma.sync m16n8k16 forms the 16-element block dot
@@ -25,7 +27,7 @@
 // and the block scales are folded exactly into the fp16 weight operand, so the MMAs accumulate straight over K.
 // Activations are converted BF16 -> fp16 per token with an exact power-of-two scale taken from the token's amax:
 // a dedicated warp bulk-copies the raw rows of the next projection into one of two buffers (under the tiles of the
-// projection before), and the sixteen consumer warps convert them in place when they get there, each a slice of
+// projection before), and the consumer warps convert them in place when they get there, each a slice of
 // one token, meeting twice on bounded mbarriers (amax known, conversion done).
 //
 // All waits are bounded; on expiry a code is written to the batch's status word.
@@ -47,8 +49,17 @@ constexpr int kCodesBytes = kTileRows * kStepBytes;
 constexpr int kScaleBytes = 4 * 512;
 constexpr int kStageBytes = kCodesBytes + kScaleBytes;
 constexpr int kRowGroups = 8;                   // 16-row groups per tile
-constexpr int kConsumerWarps = 16;              // each row group is shared by two warps that split the K step
-constexpr int kThreads = (2 + kConsumerWarps) * 32;  // warp 0 producer, warp 1 activation copies, 16 consumers
+// Two shapes of CTA.  KS = 1: eight consumer warps, one per 16-row group, each taking the whole K step; 112 KB of
+// shared memory, so that two CTAs share an SM and each one's stalls (change of projection, tile hand-over, epilogue)
+// run under the other's arithmetic.  KS = 2: sixteen consumer warps, two per row group splitting every K step (their
+// partial sums meet in shared memory at the end of a tile); one CTA per SM with all of its shared memory, for
+// activations too large for the first shape.
+__host__ __device__ constexpr int consumer_warps(int ks) { return kRowGroups * ks; }
+__host__ __device__ constexpr int cta_threads(int ks) { return (2 + consumer_warps(ks)) * 32; }  // warp 0 producer, warp 1 activation copies
+__host__ __device__ constexpr int ctas_per_sm(int ks) { return ks == 1 ? 2 : 1; }
+__host__ __device__ constexpr int smem_budget(int ks) { return ks == 1 ? 112 * 1024 : 227 * 1024; }
+// floats of the buffer in which the two warps of a row group meet (none when a warp takes the whole K step)
+__host__ __device__ constexpr int red_floats(int ks, int mt) { return ks == 2 ? 2 * kRowGroups * 32 * 4 * mt : 0; }
 constexpr int kMaxTilesInSmem = 64;             // tile descriptors staged per CTA
 constexpr int kMaxStages = 8;
 constexpr int kZeroHalfs = 320;                 // covers the 8 chunk offsets (32 halfs apart) of a K step + a bank shift
@@ -181,14 +192,18 @@ __device__ __forceinline__ float ue4m3_to_f32(uint32_t byte) {
 }
 
 // MT = number of 4-token groups (1 for M <= 4, 2 for M <= 8).
-template <int MT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int MT, int KS>
+__global__ void __launch_bounds__(cta_threads(KS), ctas_per_sm(KS))
 gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * __restrict__ tiles,
                          const int * __restrict__ cta_begin, int m_tokens, const __nv_bfloat16 * x_override,
                          __nv_bfloat16 * y_override, int stages, int x_buf_halfs, int xs_buf_floats,
                          int x_bufs, unsigned long long * item_done,
                          int counted_items, unsigned int * status, uint32_t wait_limit, unsigned int wait_extra) {
-  constexpr bool kDense = (MT == 2);  // five to eight tokens: dense MMA mapping, activations converted by the consumers
+  constexpr bool kDense = (MT == 2);  // five to eight tokens: dense MMA mapping
+  constexpr int kConsumerWarps = consumer_warps(KS);
+  constexpr int kConsumerShift = KS == 2 ? 4 : 3;  // log2(kConsumerWarps)
+  constexpr int kThreads = cta_threads(KS);
+  constexpr int kKSplit = KS;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled code tiles; pointer arithmetic on the __shared__ array (rather than an
   // integer round trip) keeps every later access a shared-memory access for the compiler.
@@ -197,7 +212,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   __half * zeros = xbuf + x_bufs * x_buf_halfs;                                   // kZeroHalfs of 0.0, 128-byte aligned
   float * xsbuf = reinterpret_cast<float *>(zeros + kZeroHalfs);                   // 2 buffers of xs_buf_floats (1/scale)
   float * red = xsbuf + 2 * xs_buf_floats;                                         // 2 x [8 row groups][32 lanes][4*MT]
-  GemvTile * stile = reinterpret_cast<GemvTile *>(red + 2 * kRowGroups * 32 * 4 * MT);
+  GemvTile * stile = reinterpret_cast<GemvTile *>(red + red_floats(KS, MT));
   uint64_t * bars = reinterpret_cast<uint64_t *>(stile + kMaxTilesInSmem);
   // bars: full[kMaxStages], empty[kMaxStages], xfull[2], xempty[2], red_full[2], red_free[2], conv[2]
   uint64_t * full = bars;
@@ -403,7 +418,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
           // shared memory.  Both meeting points are bounded mbarrier waits.
           const int tshift = m_tokens > 4 ? 3 : (m_tokens > 2 ? 2 : (m_tokens > 1 ? 1 : 0));
           const int ctoken = cw & ((1 << tshift) - 1);
-          const int khalf = tile->k >> (4 - tshift);  // columns per slice
+          const int khalf = tile->k >> (kConsumerShift - tshift);  // columns per slice
           const bool live = ctoken < m_tokens;
           __half * crow = xbuf + buf * x_buf_halfs + static_cast<size_t>(ctoken) * (tile->k + x_pad(m_tokens)) + (cw >> tshift) * khalf;
           const uint32_t par = xi & 1;
@@ -503,8 +518,8 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         const uint32_t codes_addr = smem_u32(codes) + lm_row_off;
 
 #pragma unroll
-        for (int pp = 0; pp < 2; ++pp) {
-          const int pair = 2 * kh + pp;
+        for (int pp = 0; pp < 4 / kKSplit; ++pp) {
+          const int pair = (4 / kKSplit) * kh + pp;
           uint32_t r[4];
           ldmatrix_x4(codes_addr + (((2 * pair + lm_chunk) ^ lm_xor) << 4), r[0], r[1], r[2], r[3]);
           if constexpr (kDense) {
@@ -581,7 +596,7 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
       const int rb = ti & 1;
       const uint32_t rphase = (ti >> 1) & 1;
       float * slot = red + ((rb * kRowGroups + rg) * 32 + lane) * 4 * MT;
-      if (kh == 1) {
+      if (kKSplit == 2 && kh == 1) {
         if (!mbar_wait(smem_u32(red_free + rb), rphase ^ 1, wait_limit)) {
           if (lane == 0) atomicCAS(status, 0u, kConsumerWait);
           ok = false;
@@ -593,21 +608,23 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(red_full + rb));
       } else {
-        if (!mbar_wait(smem_u32(red_full + rb), rphase, wait_limit)) {
-          if (lane == 0) atomicCAS(status, 0u, kConsumerWait);
-          ok = false;
-          break;
-        }
+        if constexpr (kKSplit == 2) {
+          if (!mbar_wait(smem_u32(red_full + rb), rphase, wait_limit)) {
+            if (lane == 0) atomicCAS(status, 0u, kConsumerWait);
+            ok = false;
+            break;
+          }
 #pragma unroll
-        for (int ts = 0; ts < kGroups; ++ts) {
-          const float4 o = *reinterpret_cast<const float4 *>(slot + 4 * ts);
-          acc[ts][0] += o.x;
-          acc[ts][1] += o.y;
-          acc[ts][2] += o.z;
-          acc[ts][3] += o.w;
+          for (int ts = 0; ts < kGroups; ++ts) {
+            const float4 o = *reinterpret_cast<const float4 *>(slot + 4 * ts);
+            acc[ts][0] += o.x;
+            acc[ts][1] += o.y;
+            acc[ts][2] += o.z;
+            acc[ts][3] += o.w;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(red_free + rb));
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(red_free + rb));
         __nv_bfloat16 * y = y_override != nullptr ? y_override : tile->y;
         const int rows = tile->rows;
         const float s2 = tile->s2;
@@ -682,7 +699,6 @@ gemv_w4a16_stream_kernel(const GemvItem * __restrict__ items, const GemvTile * _
   }
 }
 
-constexpr int kSmemBudget = 227 * 1024;
 constexpr int kBarrierBytes = (2 * kMaxStages + 8 + 2) * 8 + 2 * 8 * 4;
 
 struct Plan {
@@ -691,30 +707,65 @@ struct Plan {
   int xs_buf_floats = 0;
   int x_bufs = 0;
   int smem_bytes = 0;
+  int ksplit = 2;  // shape of the CTA (template KS)
 };
 
 // Shared-memory plan for a batch with at most max_k columns: activation buffers (raw BF16 rows land in them and are
 // converted in place, so there is no separate raw ring), then as many ring stages as fit.  Two buffers (the next
 // item's copy runs under the current item's tiles) when at least five stages remain, else one.
-bool make_plan(int m, int max_k, Plan * p) {
+bool make_plan(int m, int max_k, Plan * p, int min_ks = 1) {
   const int mt = m < kDenseFrom ? 1 : 2;
   const int x_halfs = ((m * (max_k + x_pad(m)) + 63) / 64) * 64;  // whole 128-byte bank spans
   const int xs_floats = 8;
-  const int base = 1024 + 2 * xs_floats * 4 + 2 * kRowGroups * 32 * 4 * mt * 4 + kZeroHalfs * 2 +
-                   kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
-  for (int bufs = 2; bufs >= 1; --bufs) {
-    const int fixed = base + bufs * x_halfs * 2;
-    const int stages = std::min(kMaxStages, (kSmemBudget - fixed) / kStageBytes);
-    if (stages >= (bufs == 2 ? 5 : 3)) {
-      p->stages = stages;
-      p->x_buf_halfs = x_halfs;
-      p->xs_buf_floats = xs_floats;
-      p->x_bufs = bufs;
-      p->smem_bytes = fixed + stages * kStageBytes;
-      return true;
+  // The two-CTAs-per-SM shape first (measured: 0.8B-class step at one token 51 -> 45 us); it needs four ring stages
+  // per CTA beside two activation buffers, or three beside one.  Else the one-CTA shape with all of the SM's memory.
+  for (int ks = min_ks; ks <= 2; ++ks) {
+    const int base = 1024 + 2 * xs_floats * 4 + red_floats(ks, mt) * 4 + kZeroHalfs * 2 +
+                     kMaxTilesInSmem * static_cast<int>(sizeof(GemvTile)) + kBarrierBytes;
+    for (int bufs = 2; bufs >= 1; --bufs) {
+      const int fixed = base + bufs * x_halfs * 2;
+      const int stages = std::min(kMaxStages, (smem_budget(ks) - fixed) / kStageBytes);
+      if (stages >= (bufs == 2 ? (ks == 1 ? 4 : 5) : 3)) {
+        p->stages = stages;
+        p->x_buf_halfs = x_halfs;
+        p->xs_buf_floats = xs_floats;
+        p->x_bufs = bufs;
+        p->smem_bytes = fixed + stages * kStageBytes;
+        p->ksplit = ks;
+        return true;
+      }
     }
   }
   return false;
+}
+
+using StreamKernel = void (*)(const GemvItem *, const GemvTile *, const int *, int, const __nv_bfloat16 *, __nv_bfloat16 *,
+                              int, int, int, int, unsigned long long *, int, unsigned int *, uint32_t, unsigned int);
+
+StreamKernel stream_kernel(int m, int ks) {
+  if (m < kDenseFrom) return ks == 1 ? gemv_w4a16_stream_kernel<1, 1> : gemv_w4a16_stream_kernel<1, 2>;
+  return ks == 1 ? gemv_w4a16_stream_kernel<2, 1> : gemv_w4a16_stream_kernel<2, 2>;
+}
+
+// The plan for a list on the current device: the two-CTAs-per-SM shape only if two of its CTAs really fit on an SM
+// (items that wait for other items rely on every CTA of the grid being resident).
+cudaError_t plan_for_device(int m, int max_k, Plan * p, bool * fits) {
+  *fits = make_plan(m, max_k, p);
+  if (!*fits) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(stream_kernel(m, p->ksplit), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       smem_budget(p->ksplit));
+  if (e != cudaSuccess) return e;
+  if (p->ksplit == 1) {
+    int resident = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, stream_kernel(m, 1), cta_threads(1),
+                                                      static_cast<size_t>(p->smem_bytes));
+    if (e != cudaSuccess) return e;
+    if (resident < 2) {
+      *fits = make_plan(m, max_k, p, 2);
+      if (*fits) e = cudaFuncSetAttribute(stream_kernel(m, 2), cudaFuncAttributeMaxDynamicSharedMemorySize, smem_budget(2));
+    }
+  }
+  return e;
 }
 
 }  // namespace
@@ -773,15 +824,20 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
   auto * b = new q35b_gemv_batch();
   b->count = count;
   b->m = m;
-  if (!make_plan(m, max_k, &b->plan)) {
-    delete b;
-    return fail(Q35B_ERR_SHAPE, "Activations of the NVFP4 projection work list do not fit in shared memory.");
-  }
   if (cudaGetDevice(&b->device) != cudaSuccess) {
     delete b;
     return fail_cuda(cudaGetLastError(), "cudaGetDevice");
   }
-  const int grid_max = sm_count();
+  bool fits = false;
+  if (const cudaError_t pe = plan_for_device(m, max_k, &b->plan, &fits); pe != cudaSuccess) {
+    delete b;
+    return fail_cuda(pe, "planning the projection work list");
+  }
+  if (!fits) {
+    delete b;
+    return fail(Q35B_ERR_SHAPE, "Activations of the NVFP4 projection work list do not fit in shared memory.");
+  }
+  const int grid_max = sm_count() * ctas_per_sm(b->plan.ksplit);
 
   std::vector<GemvTile> all;
   std::vector<GemvItem> h_items(count);
@@ -892,12 +948,6 @@ int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_b
   if (e == cudaSuccess) e = cudaMemcpy(b->tiles, h_tiles.data(), sizeof(GemvTile) * h_tiles.size(), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(b->cta_begin, h_begin.data(), sizeof(int) * (grid + 1), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemset(b->status, 0, 16 + sizeof(unsigned long long) * (count + 1));
-  if (e == cudaSuccess) {
-    e = cudaFuncSetAttribute(gemv_w4a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-  }
-  if (e == cudaSuccess) {
-    e = cudaFuncSetAttribute(gemv_w4a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-  }
   if (e != cudaSuccess) {
     cudaFree(b->dev_base);
     delete b;
@@ -929,7 +979,7 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   const int counted = b->has_dependencies ? b->count : 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(b->grid));
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(static_cast<unsigned>(cta_threads(b->plan.ksplit)));
   cfg.dynamicSmemBytes = static_cast<size_t>(b->plan.smem_bytes);
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
@@ -941,7 +991,7 @@ int gemv_batch_launch(const q35b_gemv_batch * b, const void * x_override, void *
   const GemvTile * d_tiles = b->tiles;
   const int * d_begin = b->cta_begin;
   const Plan & pl = b->plan;
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, b->m < kDenseFrom ? gemv_w4a16_stream_kernel<1> : gemv_w4a16_stream_kernel<2>, d_items,
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, stream_kernel(b->m, pl.ksplit), d_items,
                                             d_tiles, d_begin, b->m, xo, yo, pl.stages, pl.x_buf_halfs, pl.xs_buf_floats,
                                             pl.x_bufs, b->item_done, counted, b->status, b->wait_limit,
                                             b->wait_extra);
