@@ -184,7 +184,7 @@ Q35B_API int q35b_gemv_batch_create(const q35b_gemv_item * items, int count, int
  * left over, so their sum reproduces the activation to within 6^-digits of its block's largest element (5 digits:
  * 1.3e-4 at worst; BF16's own rounding step is 3.9e-3).  Outputs stay within the relative L2 bound of 1e-3 against
  * the exact W4A16 result.  Measured on B200 it is NOT the faster path: 73 us per 0.8B-class step at one token and
- * 96 us at eight, against 50 and 57 us for q35b_gemv_batch_create (with operand tiles this narrow the tensor pipe's
+ * 96 us at eight, against 44.5 and 57 us for q35b_gemv_batch_create (with operand tiles this narrow the tensor pipe's
  * copy-to-MMA turnaround per 256 columns of K sets the pace); it is kept as the variant whose cost does not grow
  * with the conversion work and as the decode-side user of the weight-streaming kernel.  Items must be independent
  * (after = 0); non-finite activations count as zero.  digits: 1..8 with m * digits <= 128; 5 is the intended
