@@ -753,9 +753,63 @@ def bench_mlp(args, q, torch, dist, timer, device, rank, world) -> dict:
             timer.barrier()
         exchange = ("NVFP4 intermediate columns and BF16 output columns pushed to every rank with peer-memory stores "
                     f"(q35b_peer_push) + flag waits; one CUDA graph per block")
+    token_sharded = None
+    if world > 1 and m % (128 * world) == 0:
+        # The same block with the TOKENS dealt out instead of the weight rows: every rank keeps whole weights (as
+        # the decode replicas do) and runs its M / world rows; nothing is exchanged but the activation's
+        # per-tensor scale (one float, here taken from set 0's full activation outside the timed region).
+        mr = m // world
+        rows = slice(rank * mr, (rank + 1) * mr)
+        gen2 = torch.Generator(device=device).manual_seed(77)
+        gw = [q.quantize_weight(torch.randn((inter, hidden), generator=gen2, device=device) * 0.02) for _ in range(2)]
+        dw = q.quantize_weight(torch.randn((hidden, inter), generator=gen2, device=device) * 0.02)
+        host = [(c.cpu().numpy(), s.cpu().numpy(), s2) for (c, s, s2) in gw]
+        gu_full = q.Nvfp4Weight.gate_up_from_host(*host[0], *host[1])
+        down_full = q.Nvfp4Weight.from_device(dw[0], dw[1], dw[2])
+        x_full, res_full = data[0]["x"], data[0]["res"]
+        codes, scales, g = q.quantize_activations(x_full, scratch=data[0]["sx"])
+        x_scale = float(g.item())
+        h = q.gemm_w4a4(gu_full, codes, scales, g, m)
+        hs_full = (h.float().abs().max() / (6.0 * 448.0)).reshape(1).to(torch.float32)
+        hc, hs, hg = q.gemm_w4a4_gate_up_quant(gu_full, codes, scales, g, m, hs_full)
+        expected = q.gemm_w4a4(down_full, hc, hs, hg, m, residual=res_full)[rows].clone()
+        del h, hc, hs
+        xs_ = [x_full[rows].contiguous()] + [torch.randn((mr, hidden), generator=gen2, device=device).to(torch.bfloat16)
+                                              for _ in range(MLP_SETS - 1)]
+        rs_ = [res_full[rows].contiguous()] + [torch.randn((mr, hidden), generator=gen2, device=device).to(torch.bfloat16)
+                                                for _ in range(MLP_SETS - 1)]
+        sxs = [q.act_scratch(mr, hidden, device) for _ in range(MLP_SETS)]
+        lay = sharding.MlpLayout(mr, hidden, inter)
+        tb = [(torch.empty(mr * lay.codes_ld, dtype=torch.uint8, device=device),
+               torch.empty(lay.scales_bytes, dtype=torch.uint8, device=device),
+               torch.empty((mr, hidden), dtype=torch.bfloat16, device=device)) for _ in range(MLP_SETS)]
+
+        def tblock(i):
+            hc_, hs_, y_ = tb[i]
+            c_, s_, g_ = q.quantize_activations(xs_[i], global_scale=x_scale, scratch=sxs[i])
+            c2, s2_, g2 = q.gemm_w4a4_gate_up_quant(gu_full, c_, s_, g_, mr, hs_full, scratch=(hc_, hs_, None), status=status)
+            q.gemm_w4a4(down_full, c2, s2_, g2, mr, out=y_, status=status, residual=rs_[i])
+            return y_
+        tgraphs = [capture(torch, st, lambda i=i: tblock(i)) for i in range(MLP_SETS)]
+        ti = [0]
+
+        def tone():
+            tgraphs[ti[0] % MLP_SETS].replay()
+            ti[0] += 1
+        tms = timer.per_call(st, tone, steps, 3)
+        with torch.cuda.stream(st):
+            okt = torch.tensor([int(torch.equal(tblock(0), expected) and int(status.item()) == 0)], device=device)
+            st.synchronize()
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        token_sharded = {"ms": round(tms, 4), "tflops": round(flops / (tms * 1e-3) / 1e12, 1), "tokens_per_gpu": mr,
+                         "exchange": "none: whole weights on every GPU, M / N tokens each, the per-tensor activation "
+                                     "scale (one float) agreed beforehand",
+                         "checked": bool(int(okt.item())),
+                         "check": "rows of this rank torch.equal to the same rows of the unsharded block, on every rank"}
     h_bytes = m * inter * 9 // 16
     out_bytes = m * hidden * 2
-    return {"workload": f"prefill MLP block M={m}, hidden {hidden}, intermediate {inter}, N-sharded over {world} GPU(s): "
+    return {"token_sharded": token_sharded,
+            "workload": f"prefill MLP block M={m}, hidden {hidden}, intermediate {inter}, N-sharded over {world} GPU(s): "
                         "quantise x, gate/up GEMM writing NVFP4, down GEMM + residual",
             "ms": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 1), "exchange": exchange,
             "gathered_bytes_in_per_gpu": (h_bytes + out_bytes) * (world - 1) // world,
