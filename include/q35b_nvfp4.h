@@ -211,6 +211,13 @@ Q35B_API int q35b_gemv_batch_status(const q35b_gemv_batch * batch, unsigned int 
  * 1 << 22 polls restore normal operation.)  Also clears the list's status word and completion counts. */
 Q35B_API int q35b_debug_gemv_batch_wait(q35b_gemv_batch * batch, unsigned int wait_limit_polls,
                                         unsigned int extra_completions);
+/* The shared-memory plan a work list of `m` tokens over weights of at most `max_k` columns would get (host
+ * arithmetic only, no device needed): ctas_per_sm is 2 for the shape with eight consumer warps and half an SM's
+ * shared memory, 1 for the shape with sixteen consumer warps and all of it; ring_stages are 18 KB each;
+ * activation_buffers is 1 or 2; smem_bytes is the dynamic shared memory of one CTA.  Q35B_ERR_SHAPE when the
+ * activations fit neither shape. */
+Q35B_API int q35b_debug_gemv_plan(int m, int max_k, int * ctas_per_sm, int * ring_stages, int * activation_buffers,
+                                  int * smem_bytes);
 /* Weight bytes (codes + scales) one run streams. */
 Q35B_API size_t q35b_gemv_batch_stream_bytes(const q35b_gemv_batch * batch);
 

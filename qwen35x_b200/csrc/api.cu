@@ -350,6 +350,10 @@ int q35b_gemv_batch_status(const q35b_gemv_batch * batch, unsigned int * status_
   return gemv_batch_read_status(batch, status_out);
 }
 
+int q35b_debug_gemv_plan(int m, int max_k, int * ctas_per_sm, int * ring_stages, int * activation_buffers, int * smem_bytes) {
+  return q35b::gemv_plan_debug(m, max_k, ctas_per_sm, ring_stages, activation_buffers, smem_bytes);
+}
+
 int q35b_debug_gemv_batch_wait(q35b_gemv_batch * batch, unsigned int wait_limit_polls, unsigned int extra_completions) {
   return gemv_batch_debug_wait(batch, wait_limit_polls, extra_completions);
 }

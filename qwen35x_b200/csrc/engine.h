@@ -112,6 +112,7 @@ int gemv_batch_launch(const struct q35b_gemv_batch * b, const void * x_override,
 void gemv_batch_free(struct q35b_gemv_batch * b);
 int gemv_batch_read_status(const struct q35b_gemv_batch * b, unsigned int * out);
 size_t gemv_batch_bytes(const struct q35b_gemv_batch * b);
+int gemv_plan_debug(int m, int max_k, int * ctas_per_sm, int * ring_stages, int * activation_buffers, int * smem_bytes);
 int gemv_batch_debug_wait(struct q35b_gemv_batch * b, unsigned int wait_limit, unsigned int extra_completions);
 
 // gemm_w4a4_tcgen05.cu

@@ -800,6 +800,17 @@ bool gemv_stream_eligible(const q35b_weight * w, int m) {
   return make_plan(m, w->k, &p);
 }
 
+int gemv_plan_debug(int m, int max_k, int * ctas, int * ring_stages, int * activation_buffers, int * smem_bytes) {
+  if (m < 1 || m > 8 || max_k < 256 || (max_k % 256) != 0) return fail(Q35B_ERR_SHAPE, "NVFP4 decode projection supports 1..8 tokens and cols that are a multiple of 256.");
+  Plan p;
+  if (!make_plan(m, max_k, &p)) return fail(Q35B_ERR_SHAPE, "Activations of the NVFP4 projection work list do not fit in shared memory.");
+  if (ctas != nullptr) *ctas = ctas_per_sm(p.ksplit);
+  if (ring_stages != nullptr) *ring_stages = p.stages;
+  if (activation_buffers != nullptr) *activation_buffers = p.x_bufs;
+  if (smem_bytes != nullptr) *smem_bytes = p.smem_bytes;
+  return Q35B_OK;
+}
+
 int gemv_batch_build(const q35b_gemv_item * items, int count, int m, q35b_gemv_batch ** out) {
   if (items == nullptr || out == nullptr || count <= 0) return fail(Q35B_ERR_ARGUMENT, "Invalid NVFP4 projection work list.");
   if (m < 1 || m > 8) return fail(Q35B_ERR_SHAPE, "NVFP4 decode projection supports 1..8 tokens.");

@@ -74,6 +74,8 @@ def lib() -> C.CDLL:
     L.q35b_gemv_batch_destroy.argtypes = [vp]
     L.q35b_gemv_batch_status.restype = i
     L.q35b_gemv_batch_status.argtypes = [vp, C.POINTER(C.c_uint)]
+    L.q35b_debug_gemv_plan.restype = i
+    L.q35b_debug_gemv_plan.argtypes = [i, i, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]
     L.q35b_debug_gemv_batch_wait.restype = i
     L.q35b_debug_gemv_batch_wait.argtypes = [vp, C.c_uint, C.c_uint]
     L.q35b_gemv_batch_stream_bytes.restype = sz
@@ -371,6 +373,13 @@ def quantize_activations(x, global_scale: float = 0.0, scratch=None):
     _check(fn(x.data_ptr(), m, k, global_scale, codes.data_ptr(), scales.data_ptr(), g.data_ptr(), ws.data_ptr(),
               _stream_ptr(torch)))
     return codes.view(m, k // 2), scales, g
+
+
+def gemv_plan(m: int, max_k: int) -> dict:
+    """Shared-memory plan of a decode work list (q35b_debug_gemv_plan): host arithmetic, needs no device."""
+    v = [C.c_int(0) for _ in range(4)]
+    _check(lib().q35b_debug_gemv_plan(m, max_k, *[C.byref(x) for x in v]))
+    return {"ctas_per_sm": v[0].value, "ring_stages": v[1].value, "activation_buffers": v[2].value, "smem_bytes": v[3].value}
 
 
 def gemm_default_status() -> int:

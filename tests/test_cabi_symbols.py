@@ -102,3 +102,40 @@ def test_sharded_shape_report_renders_markdown():
     assert "N-sharded over 4 x B200" in md
     assert "| cell | 4096 | 18432 | 2560 | 4608 | 33.00 | 11712.0 | 0.325 | 55.00 | yes | 147.1 |" in md
 
+
+def test_decode_work_list_plans_without_gpu():
+    """The shared-memory plan of the decode work list (host arithmetic): which of the two CTA shapes a list gets and
+    how deep its ring is, for the token counts and column counts of the benchmark configurations."""
+    import pytest
+
+    from qwen35x_b200 import engine
+
+    # 0.8B-class step (largest K = 3584): two CTAs per SM up to seven tokens, the whole SM for eight
+    for m in (1, 2, 3, 4):
+        p = engine.gemv_plan(m, 3584)
+        assert p["ctas_per_sm"] == 2 and p["ring_stages"] >= 3 and p["smem_bytes"] <= 112 * 1024, (m, p)
+    assert engine.gemv_plan(1, 3584)["activation_buffers"] == 2
+    p8 = engine.gemv_plan(8, 3584)
+    assert p8["ctas_per_sm"] == 1 and p8["ring_stages"] >= 5 and p8["activation_buffers"] == 2 and p8["smem_bytes"] <= 227 * 1024
+    # 4B-class step (largest K = 9216): one and two tokens fit half an SM, eight tokens leave the whole SM three stages
+    assert engine.gemv_plan(1, 9216)["ctas_per_sm"] == 2
+    assert engine.gemv_plan(2, 9216)["ctas_per_sm"] == 2
+    p = engine.gemv_plan(8, 9216)
+    assert p == {"ctas_per_sm": 1, "ring_stages": 3, "activation_buffers": 1, "smem_bytes": p["smem_bytes"]} and p["smem_bytes"] <= 227 * 1024
+    # every plan respects its budget; more tokens never get a deeper ring at the same shape
+    for k in (1024, 2560, 4096, 9216):
+        last = None
+        for m in range(1, 9):
+            p = engine.gemv_plan(m, k)
+            assert p["smem_bytes"] <= (112 if p["ctas_per_sm"] == 2 else 227) * 1024
+            assert p["ring_stages"] >= 3
+            if last is not None and last["ctas_per_sm"] == p["ctas_per_sm"] and last["activation_buffers"] == p["activation_buffers"]:
+                assert p["ring_stages"] <= last["ring_stages"]
+            last = p
+    with pytest.raises(engine.Q35bError):
+        engine.gemv_plan(9, 1024)
+    with pytest.raises(engine.Q35bError):
+        engine.gemv_plan(1, 1000)
+    with pytest.raises(engine.Q35bError):
+        engine.gemv_plan(8, 16384)  # 8 x 16384 fp16 activations do not fit an SM
+
