@@ -16,8 +16,11 @@
  * oracle/_ref by oracle/build_oracle.py, see tests/test_oracle_vs_reference.py)
  * and against committed golden vectors generated from them.  The W4A4 GEMM
  * expected value has no asserting counterpart in the reference (its cuBLASLt
- * call is only reported, never checked), so that one function is
- * "parity unpinned" beyond the formula at cuda_bench.cu:872-884.
+ * call is only reported, never checked); it is pinned to an OUTPUT of the
+ * reference instead: run_nvfp4_cublaslt_prefill_projection_device_bf16
+ * (cuda_bench.cu:1056-1167) run on the GPU box agrees with the engine's GEMM,
+ * which tests/test_gemm_gpu.py holds to this function, to relative L2 1e-3
+ * (tests/test_reference_gpu.py); the formula followed is cuda_bench.cu:872-884.
  *
  * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (no fused
  * multiply-add contraction: results must be bit-identical to IEEE fp32 code
@@ -364,8 +367,9 @@ Q35O_API void q35o_quantize_nvfp4(const void *x, int x_is_bf16, int rows, int co
  * with each term evaluated in fp32 in that order and accumulated in double.
  * a_codes [m, cols/2], a_scales row-major [m, cols/16], input_scale = the
  * activation tensor's global scale g.  Output rows [n_begin, n_end) of every
- * token: c_f32 / c_bf16 are [m, n_end - n_begin].  Parity unpinned: the
- * reference asserts nothing at this boundary (see the file header). */
+ * token: c_f32 / c_bf16 are [m, n_end - n_begin].  The reference asserts
+ * nothing at this boundary; pinned through its cuBLASLt bridge's output on the
+ * GPU box (see the file header). */
 Q35O_API void q35o_gemm_w4a4(const uint8_t *w_codes, const uint8_t *w_scales, float s2, int rows, int cols,
                              const uint8_t *a_codes, const uint8_t *a_scales, float input_scale, int m,
                              int n_begin, int n_end, float *c_f32, uint16_t *c_bf16, int threads) {
