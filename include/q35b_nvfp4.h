@@ -263,15 +263,16 @@ Q35B_API int q35b_quantize_nvfp4_bf16_reference_recipe(const void * x_bf16, int 
  * and the fp32->bf16 pass after it (src/kernels/cuda/prefill.cu:639).
  * Requires k % 64 == 0.  status_dev: 4 bytes of device memory, zero on entry,
  * nonzero afterwards if a bounded device-side wait expired.  With status_dev
- * NULL the call uses a word inside the library (one per device, cleared on the
- * stream ahead of the launch, nothing allocated); q35b_gemm_default_status
- * reads it.  Calls that share that word and overlap on the GPU can clear each
- * other's code: pass an own word where that matters. */
+ * NULL the call uses a word inside the library (one per device, nothing
+ * allocated, nothing launched in front of the kernel): a code stays in it until
+ * q35b_gemm_default_status reads it, which also clears it.  All calls of a
+ * device without an own word share it: pass one where the call that failed
+ * has to be told apart. */
 Q35B_API int q35b_gemm_w4a4_bf16(const q35b_weight * w, const uint8_t * a_codes, const uint8_t * a_scales_tiled,
                                  const float * input_scale_dev, int m, void * c_bf16, int ldc,
                                  unsigned int * status_dev, q35b_stream stream);
 
-/* Copies the library's status word of the current device to the host (synchronises the device). */
+/* Copies the library's status word of the current device to the host (synchronises the device) and clears it. */
 Q35B_API int q35b_gemm_default_status(unsigned int * status_out);
 
 /* Same GEMM with the residual add fused into the epilogue: c = bf16(projection + residual), residual [m, rows] BF16

@@ -433,6 +433,7 @@ extern "C" int q35b_gemm_default_status(unsigned int * status_out) {
   unsigned int * word = nullptr;
   if (const int st = default_status_word(&word)) return st;
   Q35B_CUDA_TRY(cudaMemcpy(status_out, word, sizeof(unsigned int), cudaMemcpyDeviceToHost), "cudaMemcpy(default status word)");
+  if (*status_out != 0u) Q35B_CUDA_TRY(cudaMemset(word, 0, sizeof(unsigned int)), "cudaMemset(default status word)");
   return Q35B_OK;
 }
 
@@ -501,9 +502,9 @@ int launch_gemm_w4a4(const q35b_weight * w, const uint8_t * a_codes, const uint8
   if (const int st = check_weight_device(w)) return st;
   if (!w->has_maps) return fail(Q35B_ERR_ARGUMENT, "NVFP4 weight has no tensor maps (it was not built by q35b_weight_create*).");
   if (status_dev == nullptr) {
-    // the library's own word, cleared on the stream ahead of the launch (a memset node under stream capture)
+    // the library's own word: kernels only ever write a nonzero code into it, q35b_gemm_default_status reads and
+    // clears it (no memset in front of the launch: it would sit between this kernel and the one it overlaps with)
     if (const int st = default_status_word(&status_dev)) return st;
-    Q35B_CUDA_TRY(cudaMemsetAsync(status_dev, 0, sizeof(unsigned int), s), "cudaMemsetAsync(gemm status)");
   }
   // Large problems: pairs of CTAs on 256 x 256 tiles, persistent (gemm_w4a4_2cta.cu).
   if (gemm_2cta_eligible(w, m)) {

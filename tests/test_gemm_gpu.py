@@ -110,3 +110,22 @@ def test_matches_w4a16_within_activation_noise(engine, oracle):
     c = from_torch_bf16(engine.project_prefill(w, to_torch_bf16(xb)))
     y = from_torch_bf16(engine.gemv_w4a16(w, to_torch_bf16(xb)))
     assert oracle.rel_l2(oracle.bf16_to_f32(c), oracle.bf16_to_f32(y)) < 0.15
+
+
+def test_gemm_without_a_status_word_reports_into_the_library_word(engine):
+    """A call that passes no status word uses the library's own (nothing is launched in front of the kernel for it);
+    after clean runs on all three GEMM kernels the getter reads 0."""
+    import torch
+
+    for (m, n, k) in ((300, 1024, 512), (64, 512, 512), (16, 3584, 1024)):
+        _, codes, scales, s2 = make_weight(n, k, seed=n + m)
+        w = engine.Nvfp4Weight.from_host(codes, scales, s2)
+        a_codes, a_scales, g = engine.quantize_activations(to_torch_bf16(make_activations(m, k, seed=m)))
+        before = engine.launch_count()
+        c = engine.gemm_w4a4(w, a_codes, a_scales, g, m)
+        assert engine.launch_count() == before + 1
+        torch.cuda.synchronize()
+        assert c.shape == (m, n)
+        assert engine.gemm_default_status() == 0
+        w.close()
+
