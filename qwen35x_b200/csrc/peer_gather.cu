@@ -44,6 +44,7 @@ inline unsigned int * flag_words(const q35b_peer_buffer * b) { return reinterpre
 // replayed.
 __global__ void peer_gather_wait_kernel(unsigned int * flags, int world, int rank, unsigned int epoch,
                                         unsigned int * status, uint32_t limit) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched under the tail of the kernel before it
   const int r = threadIdx.x;
   __shared__ unsigned int expected;
   if (r == 0) expected = epoch != 0u ? epoch : flags[kWaitSeqWord] + 1u;
@@ -91,6 +92,7 @@ struct PushArgs {
 };
 
 __global__ void __launch_bounds__(256) peer_push_kernel(const PushArgs a) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the bytes to forward come from the kernel before
   constexpr int kUnroll = 4;
   const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
   for (int ri = 0; ri < a.n_regions; ++ri) {
@@ -246,7 +248,7 @@ int q35b_gemm_w4a4_bf16_allgather(const q35b_weight * w, const uint8_t * a_codes
     Q35B_CUDA_TRY(cudaGetLastError(), "peer_signal_kernel launch");
     return Q35B_OK;
   }
-  Q35B_CUDA_TRY(cudaMemsetAsync(gather.done_counter, 0, sizeof(unsigned int), s), "cudaMemsetAsync(gather counter)");
+  // the closing count is left at zero by the last CTA of every launch (the flag block starts zeroed): no memset here
   auto * c = reinterpret_cast<__nv_bfloat16 *>(buffers[rank]->base) + col0;
   return launch_gemm_w4a4(w, a_codes, a_scales_tiled, input_scale_dev, m, c, ldc, nullptr, 0,
                           status_dev, s, nullptr, &gather);
@@ -259,10 +261,10 @@ int q35b_peer_gather_wait(q35b_peer_buffer * const * buffers, int world, int ran
     return fail(Q35B_ERR_ARGUMENT, "Invalid rank layout for the gathering NVFP4 prefill projection.");
   }
   if (world == 1) return Q35B_OK;
-  peer_gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flag_words(buffers[rank]), world, rank, epoch,
-                                                                         status_dev, kGatherWaitLimit);
+  const cudaError_t le = launch_pdl(peer_gather_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream),
+                                    flag_words(buffers[rank]), world, rank, epoch, status_dev, kGatherWaitLimit);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "peer_gather_wait_kernel launch");
+  Q35B_CUDA_TRY(le, "peer_gather_wait_kernel launch");
   return Q35B_OK;
 }
 
@@ -304,12 +306,11 @@ int q35b_peer_push(q35b_peer_buffer * const * buffers, int world, int rank, cons
   a.epoch = epoch;
   if (world == 1) return Q35B_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  Q35B_CUDA_TRY(cudaMemsetAsync(a.done_counter, 0, sizeof(unsigned int), s), "cudaMemsetAsync(push counter)");
   // enough threads to keep every NVLink busy, few enough that the closing count stays cheap
   const unsigned long long want = (pieces + 256ull * 4 - 1) / (256ull * 4);
   const int blocks = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(want, 2ull * sm_count())));
-  peer_push_kernel<<<blocks, 256, 0, s>>>(a);
+  const cudaError_t le = launch_pdl(peer_push_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, s, a);
   count_launch();
-  Q35B_CUDA_TRY(cudaGetLastError(), "peer_push_kernel launch");
+  Q35B_CUDA_TRY(le, "peer_push_kernel launch");
   return Q35B_OK;
 }
