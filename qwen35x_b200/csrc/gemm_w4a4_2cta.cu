@@ -52,14 +52,13 @@ constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 3481
 #define Q35B_STAGES (Q35B_TILE_N == 192 ? 6 : 5)
 #endif
 constexpr int kStages = Q35B_STAGES;
-#ifndef Q35B_EPI_WARPS
-#define Q35B_EPI_WARPS (Q35B_TILE_N == 192 ? 12 : 16)
-#endif
-constexpr int kEpilogueWarps = Q35B_EPI_WARPS;  // kEpilogueWarps / 4 per TMEM lane quarter, each a column slice
-constexpr int kThreads = (2 + kEpilogueWarps) * 32;
+// Epilogue warps per CTA (template parameter of the kernel), a multiple of four: kEpilogueWarps / 4 per TMEM lane
+// quarter, each draining a column slice of the accumulator.  Sixteen for the epilogues that do arithmetic on what they
+// drain (SiLU, NVFP4 output) and for launches that forward rows to peers (their 64-column grain); eight for the plain
+// and the residual epilogue, which measured 1-5 % faster with fewer, wider warps.
+constexpr int kEpiWarpsWide = kTileN == 192 ? 12 : 16;
+constexpr int kEpiWarpsPlain = kTileN == 192 ? 12 : 8;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-constexpr int kEpiCols = kTileN / (kEpilogueWarps / 4);  // columns drained by one epilogue warp
-static_assert(kEpilogueWarps % 4 == 0 && kEpiCols % 32 == 0 && kEpiCols * (kEpilogueWarps / 4) == kTileN, "epilogue column split");
 static_assert(kStages * kStageBytes + 1024 + 256 <= 227 * 1024, "shared memory");
 constexpr int kAccCols = kAccs * kTileN;
 constexpr int kSfaCols = kMmaPerStage * 4;
@@ -176,11 +175,14 @@ __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+template <int kEpilogueWarps>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((2 + kEpilogueWarps) * 32, 1)
 gemm_w4a4_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                       const float * __restrict__ g_dev, const GemmEpilogue ep, int m, int n, int k_bytes, int m_tiles, int num_tiles,
                       __nv_bfloat16 * __restrict__ c, int ldc, unsigned int * status) {
+  constexpr int kEpiCols = kTileN / (kEpilogueWarps / 4);  // columns drained by one epilogue warp
+  static_assert(kEpilogueWarps % 4 == 0 && kEpiCols % 32 == 0 && kEpiCols * (kEpilogueWarps / 4) == kTileN, "epilogue column split");
   extern __shared__ uint8_t smem_raw[];
   uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t * smem_a = smem;
@@ -445,7 +447,9 @@ int launch_gemm_w4a4_2cta(const q35b_weight * w, const uint8_t * a_codes, const 
                           cudaStream_t s) {
   static std::atomic<bool> attr_set[64];
   if (!attr_set[w->device & 63].load(std::memory_order_acquire)) {
-    Q35B_CUDA_TRY(cudaFuncSetAttribute(gemm_w4a4_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+    Q35B_CUDA_TRY(cudaFuncSetAttribute(gemm_w4a4_2cta_kernel<kEpiWarpsWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                  "cudaFuncSetAttribute(2-CTA gemm smem)");
+    Q35B_CUDA_TRY(cudaFuncSetAttribute(gemm_w4a4_2cta_kernel<kEpiWarpsPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
                   "cudaFuncSetAttribute(2-CTA gemm smem)");
     attr_set[w->device & 63].store(true, std::memory_order_release);
   }
@@ -456,7 +460,11 @@ int launch_gemm_w4a4_2cta(const q35b_weight * w, const uint8_t * a_codes, const 
   const int n_tiles = (w->rows + kTileN - 1) / kTileN;
   const int num_tiles = m_tiles * n_tiles;
   const int pairs = std::max(1, std::min(num_tiles, sm_count() / 2));
-  const cudaError_t le = launch_pdl(gemm_w4a4_2cta_kernel, dim3(2 * pairs), dim3(kThreads), kSmemBytes, s, tmap_a, w->tmap2_codes,
+  // plain and residual epilogues without peers: the narrow set of epilogue warps
+  const bool plain = !ep.gate_up && ep.q_codes == nullptr && ep.n_peers == 0;
+  const int epi_warps = plain ? kEpiWarpsPlain : kEpiWarpsWide;
+  const auto kernel = plain ? gemm_w4a4_2cta_kernel<kEpiWarpsPlain> : gemm_w4a4_2cta_kernel<kEpiWarpsWide>;
+  const cudaError_t le = launch_pdl(kernel, dim3(2 * pairs), dim3((2 + epi_warps) * 32), kSmemBytes, s, tmap_a, w->tmap2_codes,
                                     tmap_sfa, w->tmap2_sf, g_dev, ep, m, w->rows, w->k / 2, m_tiles, num_tiles,
                                     static_cast<__nv_bfloat16 *>(c_bf16), ldc, status_dev);
   count_launch();
