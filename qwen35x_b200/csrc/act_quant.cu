@@ -133,7 +133,7 @@ __device__ __forceinline__ void load16<float>(const float * p, float (&v)[16]) {
 // The grid covers roundup(K/16, 4) block slots per row and rows_padded rows: slots past K and rows past `rows`
 // only produce zero scale bytes (TILED layout).
 template <typename T, int RECIPE, bool TILED>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 6)  // 39 registers, six CTAs per SM: measured 4-5 % faster than five CTAs of 45
 quantize_nvfp4_kernel(const T * __restrict__ x, int rows, int rows_padded, int k, const float * __restrict__ g_dev,
                       float g_fixed, float * __restrict__ g_out, int swap, uint8_t * __restrict__ codes,
                       uint8_t * __restrict__ scales) {
